@@ -303,3 +303,120 @@ class DebisunConfig:
 
     def __eq__(self, other):
         return isinstance(other, DebisunConfig) and self.to_dict() == other.to_dict()
+
+
+def _positive_number(value) -> bool:
+    return not isinstance(value, bool) and isinstance(value, (int, float)) and value > 0
+
+
+class LarolornConfig:
+    """Larolorn: a decoder whose layers are listed one by one in config.json, some of them running with another
+    layer's weights.
+
+    ``vocab``, ``width``, ``norm.eps``, ``residual_mult`` (what a normed branch is multiplied by on its way into the
+    stream), ``logit_scale`` and ``layers``.  A layer is a ``latent_attention`` mixer (``heads``, ``dim``,
+    ``rot_dim``, ``vdim``, ``kv_rank``, ``scale``, ``rot`` with ``base`` and ``dims``, ``mask.size`` the window) or a
+    ``parallel`` one: ``left`` a grouped attention (``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``rot``,
+    ``mask.size`` the chunk) beside ``right`` a linear attention with a fixed decay per head (``heads``, ``dim``,
+    ``vdim``, ``decay``); and a feed-forward (``mlp``: ``dense`` with ``ff`` and ``limit``, or null).
+    ``weights_of: j`` names the earlier layer whose tensors the layer runs with (cache and state stay its own).
+    The configuration is kept as the dictionary it came in; this class checks it and answers the few questions
+    the engine asks.  ``max_positions`` (not a key of the design; 2**20 unless given) only bounds a request.
+    """
+    architecture = "Larolorn"
+    model_type = "larolorn"
+
+    def __init__(self, data: dict):
+        self.data = data
+        for key in ("vocab", "width"):
+            if not _positive_int(data.get(key)):
+                raise ConfigError(f"{key} must be a positive integer, got {data.get(key)!r}")
+        eps = (data.get("norm") or {}).get("eps")
+        if not _positive_number(eps):
+            raise ConfigError(f"norm.eps must be a positive number, got {eps!r}")
+        for key in ("residual_mult", "logit_scale"):
+            value = data.get(key, 1.0)
+            if isinstance(value, bool) or not isinstance(value, (int, float)):
+                raise ConfigError(f"{key} must be a number, got {value!r}")
+        layers = data.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError("layers must be a non-empty list")
+        for index, layer in enumerate(layers):
+            where = f"layers[{index}]"
+            kind, mixer = layer.get("type"), layer.get("mixer")
+            if not isinstance(mixer, dict):
+                raise ConfigError(f"{where}.mixer must be an object")
+            if kind == "latent_attention":
+                self._check_sizes(where, mixer, ("heads", "dim", "rot_dim", "vdim", "kv_rank"))
+                self._check_rotation(where, mixer, mixer["rot_dim"])
+                if mixer["rot"]["dims"] != mixer["rot_dim"]:
+                    raise ConfigError(f"{where}: the rotated part has {mixer['rot_dim']} dimensions, rot.dims says {mixer['rot']['dims']}")
+                self._check_mask(where, mixer)
+            elif kind == "parallel":
+                left, right = mixer.get("left"), mixer.get("right")
+                if not isinstance(left, dict) or not isinstance(right, dict):
+                    raise ConfigError(f"{where}.mixer needs a left and a right mixer")
+                self._check_sizes(where + ".left", left, ("heads", "kv_heads", "dim", "vdim"))
+                if left["heads"] % left["kv_heads"]:
+                    raise ConfigError(f"{where}: {left['heads']} heads do not divide into {left['kv_heads']} kv heads")
+                self._check_rotation(where + ".left", left, left["dim"])
+                self._check_mask(where + ".left", left)
+                self._check_sizes(where + ".right", right, ("heads", "dim", "vdim"))
+                decay = right.get("decay")
+                if not isinstance(decay, list) or len(decay) != right["heads"] \
+                        or any(isinstance(v, bool) or not isinstance(v, (int, float)) or not 0 <= v <= 1 for v in decay):
+                    raise ConfigError(f"{where}.right.decay must give one decay in [0, 1] per head")
+            else:
+                raise ConfigError(f"{where}.type {kind!r} is neither latent_attention nor parallel")
+            for m in ([mixer] if kind == "latent_attention" else [mixer["left"]]):
+                if not _positive_number(m.get("scale")):
+                    raise ConfigError(f"{where}: scale must be a positive number, got {m.get('scale')!r}")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") != "dense":
+                    raise ConfigError(f"{where}.mlp.kind {mlp.get('kind')!r} is not dense")
+                if not _positive_int(mlp.get("ff")) or not _positive_number(mlp.get("limit")):
+                    raise ConfigError(f"{where}.mlp needs a positive ff and limit")
+            source = layer.get("weights_of")
+            if source is not None:
+                if type(source) is not int or not 0 <= source < index or layers[source].get("weights_of") is not None:
+                    raise ConfigError(f"{where}.weights_of must name an earlier layer that has tensors of its own")
+                theirs = layers[source]
+                if any(theirs.get(k) != layer.get(k) for k in ("type", "mixer", "mlp")):
+                    raise ConfigError(f"{where} and layers[{source}] share weights but differ in type, mixer or mlp")
+        self.vocab_size, self.width, self.eps = data["vocab"], data["width"], float(eps)
+        self.residual_mult, self.logit_scale = float(data.get("residual_mult", 1.0)), float(data.get("logit_scale", 1.0))
+        self.layers = layers
+        self.max_positions = int(data.get("max_positions", 1 << 20))
+        eos = data.get("eos_token_id")
+        self.eos_token_ids = frozenset() if eos is None else frozenset(eos if isinstance(eos, list) else [eos])
+
+    @staticmethod
+    def _check_sizes(where, mixer, keys):
+        for key in keys:
+            if not _positive_int(mixer.get(key)):
+                raise ConfigError(f"{where}.{key} must be a positive integer, got {mixer.get(key)!r}")
+
+    @staticmethod
+    def _check_rotation(where, mixer, most):
+        rot = mixer.get("rot")
+        if not isinstance(rot, dict) or not _positive_number(rot.get("base")) or not _positive_int(rot.get("dims")) \
+                or rot["dims"] % 2 or rot["dims"] > most:
+            raise ConfigError(f"{where}.rot needs a positive base and an even number of dims, at most {most}; got {rot!r}")
+
+    @staticmethod
+    def _check_mask(where, mixer):
+        if not _positive_int((mixer.get("mask") or {}).get("size")):
+            raise ConfigError(f"{where}.mask.size must be a positive integer, got {mixer.get('mask')!r}")
+
+    @classmethod
+    def from_dict(cls, data: dict) -> "LarolornConfig":
+        if data.get("architecture", cls.architecture) != cls.architecture:
+            raise ConfigError(f"architecture {data.get('architecture')!r} is not {cls.architecture}")
+        return cls(json.loads(json.dumps(data)))
+
+    def to_dict(self) -> dict:
+        return json.loads(json.dumps(self.data)) | {"architecture": self.architecture}
+
+    def __eq__(self, other):
+        return isinstance(other, LarolornConfig) and self.to_dict() == other.to_dict()

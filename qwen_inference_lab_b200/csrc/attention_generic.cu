@@ -27,7 +27,9 @@
 //               table read its last entry (the caller expands buckets of distances into this table)
 //   chunk       position i sees only the j <= i with floor(i / chunk) = floor(j / chunk), chunks counted
 //               from position 0 of the sequence
-//   sink        one is added to the softmax's denominator: a key of score 0 that has no value
+//   sink        one is added to the softmax's denominator: a key of score 0 that has no value; with
+//               sink_logits (float32 [Hq]) the added term is exp(sink_logits[h]) instead: a learned score per head
+//               that is not scaled and counts once
 #include "common.cuh"
 
 struct ScoreOptions {
@@ -36,6 +38,7 @@ struct ScoreOptions {
     int dist_len;
     int chunk;                // 0: none
     int sink;                 // 0 or 1
+    const float* sink_logits; // null: the sink's score is 0
 };
 
 #define GEN_TILE 128
@@ -71,7 +74,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache
     for (int d = tid; d < head_dim; d += GEN_TILE) qs[d] = to_f32<T>(qrow[d]);
 
     // the sink is a key of score 0 and weight exp(0 - max) that adds nothing to the sum of values
-    float m_run = opt.sink ? 0.f : -INFINITY, l_run = opt.sink ? 1.f : 0.f;
+    float m_run = opt.sink ? (opt.sink_logits != nullptr ? opt.sink_logits[head] : 0.f) : -INFINITY, l_run = opt.sink ? 1.f : 0.f;
     float acc[GEN_DPT];
 #pragma unroll
     for (int i = 0; i < GEN_DPT; ++i) acc[i] = 0.f;
@@ -147,7 +150,8 @@ extern "C" int qil_attention_generic(
     const void* q, const void* kv_cache, void* out, const int* positions, const int* token_row,
     const int* block_table, int table_stride, int n_tokens, int n_q_heads, int n_kv_heads,
     int head_dim, int v_dim, int page_size, int num_pages, int window, float scale, const float* slopes,
-    float softcap, const float* dist_bias, int dist_len, int chunk, int sink, int act_dtype, cudaStream_t stream) {
+    float softcap, const float* dist_bias, int dist_len, int chunk, int sink, const float* sink_logits, int act_dtype,
+    cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (head_dim <= 0 || head_dim > GEN_MAX_D || v_dim <= 0 || v_dim > GEN_MAX_D)
         QIL_REFUSE("attention_generic: head sizes %d and %d must lie in 1..%d", head_dim, v_dim, GEN_MAX_D);
@@ -157,7 +161,7 @@ extern "C" int qil_attention_generic(
     if (page_size <= 0 || window < 0) QIL_REFUSE("attention_generic: page_size %d window %d", page_size, window);
     if (softcap < 0.f || chunk < 0 || (dist_bias != nullptr && dist_len < 1))
         QIL_REFUSE("attention_generic: softcap %g chunk %d distance table of %d", softcap, chunk, dist_len);
-    ScoreOptions opt = {softcap, dist_bias, dist_len, chunk, sink ? 1 : 0};
+    ScoreOptions opt = {softcap, dist_bias, dist_len, chunk, (sink || sink_logits != nullptr) ? 1 : 0, sink_logits};
     dim3 grid(n_tokens, n_q_heads);
     const size_t smem = (size_t)(head_dim + GEN_TILE * 33 + GEN_TILE + 32) * sizeof(float)
                         + 2 * GEN_TILE * sizeof(long long);

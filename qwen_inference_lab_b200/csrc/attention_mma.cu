@@ -101,12 +101,20 @@ struct AttnParams {
     //   dist_bias     float32 [Hq][dist_len], the learned values times log2(e): added by distance (query position -
     //                 key position), the last entry for every distance beyond the table
     //   chunk > 0     a query sees only the keys of its own chunk of that many positions (counted from position 0)
-    //   sink          one is added to the softmax's denominator (a key of score 0 without a value)
+    //   sink          one is added to the softmax's denominator (a key of score 0 without a value); with sink_log2
+    //                 (float32 [Hq], learned scores times log2(e)) the added term is exp2(sink_log2[h]) instead
     float scale, softcap;
     float tanh_arg, cap_log2;   // 2 log2(e) scale / softcap and softcap log2(e): see modified_score_log2
     const float* dist_bias;     // times log2(e)
     int dist_len, chunk, sink;
+    const float* sink_log2;     // null: the sink's score is 0
 };
+
+// The sink's term of the denominator relative to the running maximum `mx` (in units of log2).
+__device__ __forceinline__ float sink_weight(const AttnParams& p, int head, float mx) {
+    const float s = p.sink_log2 != nullptr ? __ldg(p.sink_log2 + head) : 0.f;
+    return (mx == -INFINITY) ? 1.f : exp2f(s - mx);
+}
 
 // The modified score in units of log2: cap, distance table, slope.  tanh comes from one exponential,
 // tanh(x) = 1 - 2 / (e^(2x) + 1), with the constants folded on the host: absolute error of a few 1e-7 times the cap.
@@ -334,8 +342,8 @@ __device__ __forceinline__ void attn_prefill_tile(const AttnParams& p, const int
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
     if (MOD && p.sink) {      // the sink's weight: exp2(0 - max) beside the keys' sums (one when no key was seen)
-        l_a += (m_a == -INFINITY) ? 1.f : exp2f(-m_a);
-        l_b += (m_b == -INFINITY) ? 1.f : exp2f(-m_b);
+        l_a += sink_weight(p, head, m_a);
+        l_b += sink_weight(p, head, m_b);
     }
     const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
 #pragma unroll
@@ -510,7 +518,7 @@ __device__ __forceinline__ void merge_spans_of_head(const AttnParams& p, const f
         }
         mx = new_max;
     }
-    if (p.sink) sum += (mx == -INFINITY) ? 1.f : exp2f(-mx);
+    if (p.sink) sum += sink_weight(p, head, mx);
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
 #pragma unroll
     for (int i = 0; i < COLS; ++i) {
@@ -787,7 +795,7 @@ __device__ __forceinline__ void attn_decode_span_block(
         }
         const int head = kv_head * group + g0 + r;
         if (alone) {
-            if (p.sink) sum += (mx == -INFINITY) ? 1.f : exp2f(-mx);
+            if (p.sink) sum += sink_weight(p, head, mx);
             const float inv = sum > 0.f ? 1.f / sum : 0.f;
             p.out[((size_t)n * p.n_q_heads + head) * D + col] =
                 __float2bfloat16_rn(uncovered ? __int_as_float(0x7fc00000) : acc * inv);
@@ -868,17 +876,19 @@ static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, 
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.slopes_log2 = nullptr;
-    p.scale = scale; p.softcap = 0.f; p.tanh_arg = p.cap_log2 = 0.f; p.dist_bias = nullptr; p.dist_len = 0; p.chunk = 0; p.sink = 0;
+    p.scale = scale; p.softcap = 0.f; p.tanh_arg = p.cap_log2 = 0.f; p.dist_bias = nullptr; p.dist_len = 0; p.chunk = 0; p.sink = 0; p.sink_log2 = nullptr;
     return 0;
 }
 
 // The options of the MOD kernels, checked; returns whether any is set.
-static int fill_options(AttnParams& p, float softcap, const float* dist_bias, int dist_len, int chunk, int sink) {
+static int fill_options(AttnParams& p, float softcap, const float* dist_bias, int dist_len, int chunk, int sink,
+                        const float* sink_log2 = nullptr) {
     if (softcap < 0.f || chunk < 0 || (dist_bias != nullptr && dist_len < 1))
         QIL_REFUSE("attention: softcap %g chunk %d distance table of %d", softcap, chunk, dist_len);
-    if ((softcap > 0.f || dist_bias != nullptr || chunk > 0 || sink) && p.window > 0)
+    if ((softcap > 0.f || dist_bias != nullptr || chunk > 0 || sink || sink_log2 != nullptr) && p.window > 0)
         QIL_REFUSE("attention: a window does not go with chunks, a softcap, a distance table or a sink");
-    p.softcap = softcap; p.dist_bias = dist_bias; p.dist_len = dist_len; p.chunk = chunk; p.sink = sink ? 1 : 0;
+    p.softcap = softcap; p.dist_bias = dist_bias; p.dist_len = dist_len; p.chunk = chunk;
+    p.sink = (sink || sink_log2 != nullptr) ? 1 : 0; p.sink_log2 = sink_log2;
     if (softcap > 0.f) {
         p.tanh_arg = (float)(2.0 * 1.4426950408889634 * (double)p.scale / (double)softcap);
         p.cap_log2 = (float)((double)softcap * 1.4426950408889634);
@@ -932,13 +942,13 @@ static int launch_prefill(const void* q, const void* kv, void* out, const int* t
                           const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                           int page_size, int num_pages, int window, float scale,
                           const float* slopes_log2, float softcap, const float* dist_bias, int dist_len, int chunk,
-                          int sink, cudaStream_t stream) {
+                          int sink, cudaStream_t stream, const float* sink_log2 = nullptr) {
     if (n_tiles <= 0) return 0;
     AttnParams p;
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
     p.slopes_log2 = slopes_log2;
-    if (fill_options(p, softcap, dist_bias, dist_len, chunk, sink)) return -1;
+    if (fill_options(p, softcap, dist_bias, dist_len, chunk, sink, sink_log2)) return -1;
     if (n_tiles > 65535) QIL_REFUSE("attention: %d query tiles in one launch; at most 65535", n_tiles);
     if ((uintptr_t)tile_info & 15) QIL_REFUSE("attention: tile_info must be 16-byte aligned");
     const int smem = ((Q_IN_REGS ? 0 : Q_TILE) + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
@@ -968,9 +978,9 @@ extern "C" int qil_attn_prefill_modified(const void* q, const void* kv, void* ou
                                          const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                                          int page_size, int num_pages, float scale, const float* slopes_log2,
                                          float softcap, const float* dist_bias, int dist_len, int chunk, int sink,
-                                         cudaStream_t stream) {
+                                         const float* sink_log2, cudaStream_t stream) {
     return launch_prefill(q, kv, out, tile_info, n_tiles, block_table, table_stride, n_q_heads, n_kv_heads, page_size,
-                          num_pages, 0, scale, slopes_log2, softcap, dist_bias, dist_len, chunk, sink, stream);
+                          num_pages, 0, scale, slopes_log2, softcap, dist_bias, dist_len, chunk, sink, stream, sink_log2);
 }
 
 extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
@@ -994,13 +1004,14 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
                          const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                          int page_size, int num_pages, int window, float scale, const DecodeTail& tail,
                          cudaStream_t stream, const float* slopes_log2 = nullptr, float softcap = 0.f,
-                         const float* dist_bias = nullptr, int dist_len = 0, int chunk = 0, int sink = 0) {
+                         const float* dist_bias = nullptr, int dist_len = 0, int chunk = 0, int sink = 0,
+                         const float* sink_log2 = nullptr) {
     if (n_decode <= 0) return 0;
     AttnParams p;
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
     p.slopes_log2 = slopes_log2;
-    if (fill_options(p, softcap, dist_bias, dist_len, chunk, sink)) return -1;
+    if (fill_options(p, softcap, dist_bias, dist_len, chunk, sink, sink_log2)) return -1;
     if (check_decode_span(span_len, n_spans)) return -1;
     if (part_o == nullptr || part_ml == nullptr) QIL_REFUSE("attention: decode needs scratch for %d spans", n_spans);
     if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention: decode_info must be 16-byte aligned");
@@ -1051,11 +1062,11 @@ extern "C" int qil_attn_decode_modified(const void* q, const void* kv, void* out
                                         const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                                         int page_size, int num_pages, float scale, const float* slopes_log2,
                                         float softcap, const float* dist_bias, int dist_len, int chunk, int sink,
-                                        cudaStream_t stream) {
+                                        const float* sink_log2, cudaStream_t stream) {
     DecodeTail none = {};
     return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, tickets, n_spans, span_len, block_table,
                          table_stride, n_q_heads, n_kv_heads, page_size, num_pages, 0, scale, none, stream, slopes_log2,
-                         softcap, dist_bias, dist_len, chunk, sink);
+                         softcap, dist_bias, dist_len, chunk, sink, sink_log2);
 }
 
 // The same over the raw output of the query/key/value projection, for steps in which every token is a single

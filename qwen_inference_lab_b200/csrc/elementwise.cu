@@ -378,3 +378,17 @@ extern "C" int qil_fill_normal(void* out, int out_dtype, long long total, unsign
     QIL_DISPATCH_1(out_dtype, fill_normal_kernel<T><<<grid, 256, 0, stream>>>((T*)out, total, seed, std, mean));
     QIL_CHECK_LAUNCH();
 }
+
+// ---------------------------------------------------------------- x *= s (float32 rows, e.g. logits)
+__global__ void scale_inplace_kernel(float* __restrict__ x, size_t total, float s) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) x[i] *= s;
+}
+
+extern "C" int qil_scale_inplace(float* x, long long total, float s, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    scale_inplace_kernel<<<blocks, 256, 0, stream>>>(x, (size_t)total, s);
+    QIL_CHECK_LAUNCH();
+}

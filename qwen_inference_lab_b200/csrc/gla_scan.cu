@@ -26,6 +26,12 @@
 //
 // q, k, v, g and low are column ranges of one row-major buffer (the stacked projection), given as
 // pointers to their first column and the common row stride.
+//
+// Two options serve linear attention with a fixed decay per head, S_t = decay_h S_(t-1) + k_t v_t^T:
+// `head_decay` (float32 [heads]) stands in for the per-token decays, and `qkv_act` 1 applies silu to q, k
+// and v as they are read (in float32).  Such a design norms all heads' outputs together: `force_raw` sends
+// the un-normed outputs to the float32 scratch buffer whatever the sizes, and lin_norm_gate_whole
+// finishes them (one norm over a token's whole row, times sigmoid of the gate).
 #include "common.cuh"
 
 #define GLA_TB 8
@@ -81,6 +87,8 @@ __device__ __forceinline__ void gla_norm_gate_rows(const float* o_rows, int o_st
     }
 }
 
+__device__ __forceinline__ float scan_input(float x, int act) { return act == 1 ? x / (1.f + expf(-x)) : x; }
+
 #define GLA_WHOLE 0        // from the state slot, outputs, state written back
 #define GLA_OWN_STATE 1    // from zero, no outputs; the chunk's state and the product of its decays are written
 #define GLA_FROM_STATE 2   // from the given state, outputs, nothing written back
@@ -88,8 +96,8 @@ __device__ __forceinline__ void gla_norm_gate_rows(const float* o_rows, int o_st
 template <typename T, typename W, bool FUSED, int MODE>
 __global__ void __launch_bounds__(GLA_THREADS, GLA_MIN_BLOCKS)
 gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ g,
-                const float* __restrict__ alpha, int ld, float q_scale, const W* __restrict__ norm_w, float eps,
-                float* __restrict__ state, float* __restrict__ decay_product, const int* __restrict__ seg_start,
+                const float* __restrict__ alpha, const float* __restrict__ head_decay, int qkv_act, int ld, float q_scale,
+                const W* __restrict__ norm_w, float eps, float* __restrict__ state, float* __restrict__ decay_product, const int* __restrict__ seg_start,
                 const int* __restrict__ seg_len, const int* __restrict__ seg_row, int n_heads, int d, int e,
                 int ds_count, int tile_cols, float* __restrict__ o_raw, T* __restrict__ out) {
     constexpr int R = GLA_R;
@@ -130,13 +138,14 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
             const int to = tb * stride + (dd / R) * (R + 4) + dd % R;
             const bool real = dd < d;           // rows past d: zeros, which keep their (zero) state rows zero
             const size_t at = (size_t)(first + t0 + tb) * ld + head * d + dd;
-            if (MODE != GLA_OWN_STATE) sq[to] = real ? to_f32<T>(q[at]) * q_scale : 0.f;
-            sk[to] = real ? to_f32<T>(k[at]) : 0.f;
-            sa[to] = real ? alpha[(size_t)(first + t0 + tb) * n_heads * d + head * d + dd] : 0.f;
+            if (MODE != GLA_OWN_STATE) sq[to] = real ? scan_input(to_f32<T>(q[at]), qkv_act) * q_scale : 0.f;
+            sk[to] = real ? scan_input(to_f32<T>(k[at]), qkv_act) : 0.f;
+            sa[to] = !real ? 0.f : head_decay != nullptr ? head_decay[head]
+                                                         : alpha[(size_t)(first + t0 + tb) * n_heads * d + head * d + dd];
         }
         for (int i = tid; i < nb * tile_cols; i += threads) {
             const int tb = i / tile_cols, c = col0 + i % tile_cols;
-            sv[i] = c < e ? to_f32<T>(v[(size_t)(first + t0 + tb) * ld + head * e + c]) : 0.f;
+            sv[i] = c < e ? scan_input(to_f32<T>(v[(size_t)(first + t0 + tb) * ld + head * e + c]), qkv_act) : 0.f;
         }
         __syncthreads();
         if (MODE == GLA_OWN_STATE) {
@@ -240,14 +249,14 @@ gla_norm_gate_kernel(const float* __restrict__ o_raw, const T* __restrict__ g, i
 
 template <typename T, typename W, bool FUSED, int MODE>
 static cudaError_t gla_launch(dim3 grid, int threads, size_t smem, cudaStream_t stream, const void* q, const void* k,
-                              const void* v, const void* g, const float* alpha, int ld, float q_scale,
-                              const void* norm_w, float eps, float* state,
+                              const void* v, const void* g, const float* alpha, const float* head_decay, int qkv_act,
+                              int ld, float q_scale, const void* norm_w, float eps, float* state,
                               float* decay_product, const int* seg_start, const int* seg_len, const int* seg_row, int n_heads, int d, int e,
                               int ds_count, int tile_cols, float* o_raw, void* out) {
     cudaError_t err = cudaFuncSetAttribute(gla_scan_kernel<T, W, FUSED, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return err;
     return qil_launch_chained(gla_scan_kernel<T, W, FUSED, MODE>, grid, dim3(threads), smem, stream,
-                              (const T*)q, (const T*)k, (const T*)v, (const T*)g, alpha, ld, q_scale,
+                              (const T*)q, (const T*)k, (const T*)v, (const T*)g, alpha, head_decay, qkv_act, ld, q_scale,
                               (const W*)norm_w, eps, state, decay_product,
                               seg_start, seg_len,
                               seg_row, n_heads, d, e, ds_count, tile_cols, o_raw, (T*)out);
@@ -261,8 +270,8 @@ extern "C" int qil_gla_scan_needs_scratch(int d, int e) {
     return ds_count > 32 ? -1 : (e > GLA_THREADS / ds_count ? 1 : 0);
 }
 
-extern "C" int qil_gla_scan(const void* q, const void* k, const void* v, const void* g, const float* alpha, int ld,
-                            float q_scale, const void* norm_w, float eps, float* state, const int* seg_start, const int* seg_len,
+extern "C" int qil_gla_scan(const void* q, const void* k, const void* v, const void* g, const float* alpha,
+                            const float* head_decay, int qkv_act, int force_raw, int ld, float q_scale, const void* norm_w, float eps, float* state, const int* seg_start, const int* seg_len,
                             const int* seg_row, int n_segments, int n_tokens, int n_heads, int d, int e, float* o_raw,
                             void* out, int mode, float* decay_product, int act_dtype, int weight_dtype,
                             cudaStream_t stream) {
@@ -270,7 +279,7 @@ extern "C" int qil_gla_scan(const void* q, const void* k, const void* v, const v
     // [chunks, heads, d]); GLA_FROM_STATE (state and seg_row as before; the states are read only)
     if (n_segments <= 0) return 0;
     if (mode < 0 || mode > 2 || (mode == GLA_OWN_STATE && decay_product == nullptr)) QIL_REFUSE("gla_scan: mode %d", mode);
-    if (n_heads <= 0 || d <= 0 || e <= 0 || alpha == nullptr || n_segments > 65535)
+    if (n_heads <= 0 || d <= 0 || e <= 0 || (alpha == nullptr) == (head_decay == nullptr) || n_segments > 65535)
         QIL_REFUSE("gla_scan: heads %d sizes %d/%d segments %d", n_heads, d, e, n_segments);
     // a thread holds GLA_R rows of one column; ds_count threads (a power of two within a warp) share a column
     int ds_count = 1;
@@ -278,7 +287,7 @@ extern "C" int qil_gla_scan(const void* q, const void* k, const void* v, const v
     if (ds_count > 32) QIL_REFUSE("gla_scan: %d key channels per head are more than %d", d, 32 * GLA_R);
     const int tile_cols = e < GLA_THREADS / ds_count ? e : GLA_THREADS / ds_count;
     const int tiles = (e + tile_cols - 1) / tile_cols;
-    const bool fused = tiles == 1;
+    const bool fused = tiles == 1 && !force_raw;
     if (!fused && o_raw == nullptr && mode != GLA_OWN_STATE) QIL_REFUSE("gla_scan: %d value columns per head need the scratch buffer", e);
     const int threads = (tile_cols * ds_count + 31) / 32 * 32;
     const size_t smem = ((size_t)GLA_TB * (3 * ds_count * (GLA_R + 4) + 2 * tile_cols) + d) * sizeof(float);
@@ -286,7 +295,7 @@ extern "C" int qil_gla_scan(const void* q, const void* k, const void* v, const v
     cudaError_t err = cudaSuccess;
 #define QIL_GLA_GO(F, M)                                                                                         \
     QIL_DISPATCH_2(act_dtype, weight_dtype,                                                                      \
-        (err = gla_launch<T, W, F, M>(grid, threads, smem, stream, q, k, v, g, alpha, ld,                 \
+        (err = gla_launch<T, W, F, M>(grid, threads, smem, stream, q, k, v, g, alpha, head_decay, qkv_act, ld,              \
                                       q_scale, norm_w, eps, state, decay_product, seg_start, seg_len, seg_row, n_heads, \
                                       d, e, ds_count, tile_cols, o_raw, out)))
     if (mode == GLA_OWN_STATE) QIL_GLA_GO(false, GLA_OWN_STATE);
@@ -330,5 +339,37 @@ extern "C" int qil_gla_decay(const void* low, int ld, const void* a2, const void
     QIL_DISPATCH_2(act_dtype, weight_dtype,
         qil_launch_chained(gla_decay_kernel<T, W>, dim3(n_tokens), dim3(256), rank * sizeof(float), stream, (const T*)low, ld,
                            (const W*)a2, (const W*)a2_bias, rank, 1.f / tau, channels, alpha));
+    QIL_CHECK_LAUNCH();
+}
+
+// out[n][i] = o_raw[n][i] / sqrt(mean_i(o_raw[n]^2) + eps) * w[i] * sigmoid(g[n][i]) over a token's whole row of
+// `width` = heads * e values: the finish of a linear attention whose heads are normed together.
+template <typename T, typename W>
+__global__ void __launch_bounds__(256)
+lin_norm_gate_whole_kernel(const float* __restrict__ o_raw, const T* __restrict__ g, int ld, const W* __restrict__ norm_w,
+                           float eps, int width, T* __restrict__ out) {
+    __shared__ float scratch[32];
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const size_t token = blockIdx.x;
+    const float* o = o_raw + token * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += 256) ss = fmaf(o[i], o[i], ss);
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += 256) {
+        const float gate = to_f32<T>(g[token * ld + i]);
+        out[token * width + i] = from_f32<T>(o[i] * scale * to_f32<W>(norm_w[i]) * (1.f / (1.f + expf(-gate))));
+    }
+}
+
+extern "C" int qil_lin_norm_gate_whole(const float* o_raw, const void* g, int ld, const void* norm_w, float eps,
+                                       int n_tokens, int width, void* out, int act_dtype, int weight_dtype,
+                                       cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (width <= 0) QIL_REFUSE("lin_norm_gate_whole: width %d", width);
+    QIL_DISPATCH_2(act_dtype, weight_dtype,
+        qil_launch_chained(lin_norm_gate_whole_kernel<T, W>, dim3(n_tokens), dim3(256), 0, stream, o_raw, (const T*)g, ld,
+                           (const W*)norm_w, eps, width, (T*)out));
     QIL_CHECK_LAUNCH();
 }

@@ -151,3 +151,81 @@ extern "C" int qil_rms_scale_add(void* x, int x_dtype, const void* y, int y_dtyp
 #undef QIL_NORM_GO
     QIL_CHECK_LAUNCH();
 }
+
+// A branch joins the stream through a norm on the branch: x += mult * rms(a; w), rms(a; w) = a / sqrt(mean(a^2) + eps) * w.
+// With a second branch b the two are first normed with weights of their own and averaged:
+//   y = pre * (rms(a; wa) + rms(b; wb)),   x += mult * rms(y; w).
+// float32 arithmetic throughout; x is the stream (float32 or bfloat16), a and b share a type.
+template <typename TX, typename TA, typename W>
+__global__ void __launch_bounds__(256)
+rms_join_kernel(TX* __restrict__ x, const TA* __restrict__ a, const W* __restrict__ wa, const TA* __restrict__ b,
+                const W* __restrict__ wb, const W* __restrict__ w, int width, float eps, float pre, float mult) {
+    extern __shared__ float y[];             // [width] when there are two branches
+    __shared__ float scratch[32];
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const TA* ra = a + (size_t)blockIdx.x * width;
+    TX* dst = x + (size_t)blockIdx.x * width;
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < width; i += 256) {
+        const float v = to_f32<TA>(ra[i]);
+        sa = fmaf(v, v, sa);
+    }
+    sa = block_sum(sa, scratch);
+    const float scale_a = 1.0f / sqrtf(sa / (float)width + eps);
+    if (b == nullptr) {
+        for (int i = threadIdx.x; i < width; i += 256)
+            dst[i] = from_f32<TX>(to_f32<TX>(dst[i]) + mult * (to_f32<TA>(ra[i]) * scale_a * to_f32<W>(w[i])));
+        return;
+    }
+    const TA* rb = b + (size_t)blockIdx.x * width;
+    for (int i = threadIdx.x; i < width; i += 256) {
+        const float v = to_f32<TA>(rb[i]);
+        sb = fmaf(v, v, sb);
+    }
+    sb = block_sum(sb, scratch);
+    const float scale_b = 1.0f / sqrtf(sb / (float)width + eps);
+    float sy = 0.f;
+    for (int i = threadIdx.x; i < width; i += 256) {
+        const float v = pre * (to_f32<TA>(ra[i]) * scale_a * to_f32<W>(wa[i]) + to_f32<TA>(rb[i]) * scale_b * to_f32<W>(wb[i]));
+        y[i] = v;
+        sy = fmaf(v, v, sy);
+    }
+    sy = block_sum(sy, scratch);
+    const float scale_y = 1.0f / sqrtf(sy / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += 256)         // a thread reads back what it wrote itself
+        dst[i] = from_f32<TX>(to_f32<TX>(dst[i]) + mult * (y[i] * scale_y * to_f32<W>(w[i])));
+}
+
+extern "C" int qil_rms_join(void* x, int x_dtype, const void* a, const void* wa, const void* b, const void* wb,
+                            int branch_dtype, const void* w, int weight_dtype, int n_rows, int width, float eps,
+                            float pre, float mult, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (width <= 0 || width > 40960) QIL_REFUSE("rms_join: width %d", width);
+    if (b != nullptr && (wa == nullptr || wb == nullptr)) QIL_REFUSE("rms_join: two branches need a weight each");
+    const size_t smem = b != nullptr ? (size_t)width * sizeof(float) : 0;
+    cudaError_t err = cudaSuccess;
+#define QIL_JOIN_GO(TX, TA, WT)                                                                                   \
+    do {                                                                                                          \
+        if (smem > 48 * 1024)                                                                                     \
+            err = cudaFuncSetAttribute(rms_join_kernel<TX, TA, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (err == cudaSuccess)                                                                                   \
+            qil_launch_chained(rms_join_kernel<TX, TA, WT>, dim3(n_rows), dim3(256), smem, stream, (TX*)x,        \
+                               (const TA*)a, (const WT*)wa, (const TA*)b, (const WT*)wb, (const WT*)w, width, eps, \
+                               pre, mult);                                                                        \
+    } while (0)
+#define QIL_JOIN_W(TX, TA)                                                                                        \
+    do {                                                                                                          \
+        if (weight_dtype == QIL_F32) QIL_JOIN_GO(TX, TA, float); else QIL_JOIN_GO(TX, TA, bf16);                  \
+    } while (0)
+    if (weight_dtype != QIL_F32 && weight_dtype != QIL_BF16) QIL_REFUSE("rms_join: weight dtype %d", weight_dtype);
+    if (x_dtype == QIL_F32 && branch_dtype == QIL_F32) QIL_JOIN_W(float, float);
+    else if (x_dtype == QIL_F32 && branch_dtype == QIL_BF16) QIL_JOIN_W(float, bf16);
+    else if (x_dtype == QIL_BF16 && branch_dtype == QIL_BF16) QIL_JOIN_W(bf16, bf16);
+    else if (x_dtype == QIL_BF16 && branch_dtype == QIL_F32) QIL_JOIN_W(bf16, float);
+    else QIL_REFUSE("rms_join: dtypes %d += %d", x_dtype, branch_dtype);
+#undef QIL_JOIN_W
+#undef QIL_JOIN_GO
+    if (err != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(err)); return (int)err; }
+    QIL_CHECK_LAUNCH();
+}

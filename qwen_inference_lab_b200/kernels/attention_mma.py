@@ -197,10 +197,13 @@ class ScoreOptions:
     """What a design does to its scores beyond scale and causal mask, for the kernels that take it:
     ``softcap`` (score <- cap * tanh(score / cap) before any bias), ``distance_bias`` (float32 [Hq, distances] on
     the device, added by distance, the last entry for every distance beyond), ``chunk`` (a position sees the keys
-    of its own chunk of that many positions only), ``sink`` (one added to the softmax's denominator)."""
+    of its own chunk of that many positions only), ``sink`` (one added to the softmax's denominator; with
+    ``sink_logits``, float32 [Hq] on the device, exp(sink_logits[h]) instead: a learned score per head)."""
 
-    def __init__(self, softcap=0.0, distance_bias=None, chunk=0, sink=False):
-        self.softcap, self.distance_bias, self.chunk, self.sink = float(softcap or 0.0), distance_bias, int(chunk or 0), bool(sink)
+    def __init__(self, softcap=0.0, distance_bias=None, chunk=0, sink=False, sink_logits=None):
+        self.softcap, self.distance_bias, self.chunk = float(softcap or 0.0), distance_bias, int(chunk or 0)
+        self.sink, self.sink_logits = bool(sink) or sink_logits is not None, sink_logits
+        self._sink_log2 = None if sink_logits is None else (sink_logits.double() * 1.4426950408889634).float().contiguous()
         # the kernels work in units of log2: the table times log2(e), made once
         self._bias_log2 = None if distance_bias is None else (distance_bias.double() * 1.4426950408889634).float().contiguous()
 
@@ -212,11 +215,14 @@ class ScoreOptions:
         if bias is not None and (bias.dtype != torch.float32 or bias.ndim != 2 or bias.shape[0] != n_q_heads
                                  or not bias.is_cuda or not bias.is_contiguous()):
             raise KernelError("attention: the distance table must be float32 [query heads, distances] on the device")
+        sinks = self.sink_logits
+        if sinks is not None and (sinks.dtype != torch.float32 or sinks.shape != (n_q_heads,) or not sinks.is_cuda):
+            raise KernelError("attention: the sink scores must be float32 [query heads] on the device")
 
     def arguments(self):
         bias = self._bias_log2
         return (c_float(self.softcap), _p(bias), c_int(bias.shape[1] if bias is not None else 0), c_int(self.chunk),
-                c_int(1 if self.sink else 0))
+                c_int(1 if self.sink else 0), _p(self._sink_log2))
 
 
 def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_heads, head_dim, page_size, window,

@@ -18,7 +18,7 @@ _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 
 CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_f32.cu", "gemm_small_m.cu", "attention_generic.cu",
                 "sampling.cu", "norm_exact.cu", "gated_activation.cu", "qkv_store.cu", "gla_scan.cu", "moe.cu",
-                "short_conv.cu"]
+                "short_conv.cu", "rotary_freq.cu"]
 SMALL_M_MAX_ROWS = min(16, tuning.SMALL_M_MAX_ROWS)      # the kernel takes 16 at most
 
 _core = None
@@ -392,14 +392,15 @@ def check_pages(kv_cache, dtype, n_kv_heads, page_size, head_dim, v_dim, what):
 
 def attention_generic(q, kv_cache, out, positions, token_row, block_table, n_q_heads, n_kv_heads,
                       head_dim, page_size, window, scale, v_dim=None, slopes=None, softcap=0.0, distance_bias=None,
-                      chunk=0, sink=False):
+                      chunk=0, sink=False, sink_logits=None):
     """Causal GQA attention of every token over its request's pages (CUDA cores, float32 math).
 
     ``v_dim``: the size of a value head when it differs from ``head_dim`` (out is then [N, Hq * v_dim]).
     ``slopes`` float32 [Hq]: score = q.k * scale - slopes[h] * (query position - key position).
     ``softcap``: score <- softcap * tanh(score / softcap) before any bias.  ``distance_bias`` float32
     [Hq, distances]: added by distance, the last entry for every distance beyond.  ``chunk``: a position sees
-    only the keys of its own chunk of that many positions.  ``sink``: one is added to the softmax's denominator."""
+    only the keys of its own chunk of that many positions.  ``sink``: one is added to the softmax's denominator;
+    ``sink_logits`` float32 [Hq]: exp(sink_logits[h]) is added instead (a learned score per head, not scaled)."""
     v_dim = head_dim if v_dim is None else int(v_dim)
     _need(q, "q", ndim=2); _need(out, "out", q.dtype, 2)
     check_pages(kv_cache, q.dtype, n_kv_heads, page_size, head_dim, v_dim, "attention_generic")
@@ -414,6 +415,10 @@ def attention_generic(q, kv_cache, out, positions, token_row, block_table, n_q_h
         _need(distance_bias, "distance_bias", torch.float32, 2)
         if distance_bias.shape[0] != n_q_heads or distance_bias.shape[1] < 1:
             raise KernelError("attention_generic: the distance table is [query heads, distances]")
+    if sink_logits is not None:
+        _need(sink_logits, "sink_logits", torch.float32, 1)
+        if sink_logits.shape[0] != n_q_heads:
+            raise KernelError("attention_generic: one sink score per query head")
     _need(positions, "positions", torch.int32, 1); _need(token_row, "token_row", torch.int32, 1)
     _need(block_table, "block_table", torch.int32, 2)
     lib = core()
@@ -422,7 +427,7 @@ def attention_generic(q, kv_cache, out, positions, token_row, block_table, n_q_h
         c_int(n), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(v_dim), c_int(page_size),
         c_int(kv_cache.shape[0]), c_int(window), c_float(scale), _p(slopes), c_float(softcap), _p(distance_bias),
         c_int(distance_bias.shape[1] if distance_bias is not None else 0), c_int(chunk), c_int(1 if sink else 0),
-        c_int(dtype_code(q.dtype)), _stream()),
+        _p(sink_logits), c_int(dtype_code(q.dtype)), _stream()),
         "attention_generic")
     return out
 
@@ -631,7 +636,8 @@ def gla_decay(projected, low_column, a2, a2_bias, tau, out=None):
 
 
 def gla_scan(projected, columns, alpha, q_scale, norm_weight, eps, state, seg_start, seg_len, seg_row,
-             n_segments, n_heads, d, e, out, scratch=None, mode=GLA_WHOLE, decay_product=None):
+             n_segments, n_heads, d, e, out, scratch=None, mode=GLA_WHOLE, decay_product=None, head_decay=None,
+             silu_inputs=False, raw_only=False):
     """Gated linear attention over segments of a step (see csrc/gla_scan.cu for the equations).
 
     ``projected`` [N, width]: the stacked projection; ``columns`` = (q, k, v, g) first columns in it
@@ -641,14 +647,29 @@ def gla_scan(projected, columns, alpha, q_scale, norm_weight, eps, state, seg_st
     outputs then go there un-normed and ``gla_norm_gate`` finishes them.  ``mode``: GLA_WHOLE; GLA_OWN_STATE scans
     from zero and writes only the segment's own state to ``state[seg_row]`` and the product of its decays to
     ``decay_product`` [slots, n_heads, d]; GLA_FROM_STATE reads ``state[seg_row]``, writes the outputs and leaves
-    the state."""
-    _need(projected, "projected", ndim=2); _need(out, "out", projected.dtype, 2)
-    _need(alpha, "alpha", torch.float32, 2); _need(norm_weight, "norm_weight", ndim=1)
+    the state.
+
+    ``head_decay`` float32 [n_heads] (with ``alpha`` None): one fixed decay per head instead of a decay per token and
+    key channel.  ``silu_inputs``: silu on q, k and v as they are read.  ``raw_only``: the un-normed outputs go to
+    ``scratch`` whatever the sizes and nothing is normed or gated here (``out`` and ``norm_weight`` may be None)."""
+    _need(projected, "projected", ndim=2)
+    if not raw_only:
+        _need(out, "out", projected.dtype, 2); _need(norm_weight, "norm_weight", ndim=1)
+    elif scratch is None and mode != GLA_OWN_STATE:
+        raise KernelError("gla_scan: raw outputs need the scratch buffer")
+    if (alpha is None) == (head_decay is None):
+        raise KernelError("gla_scan: give the decays per token or one per head")
+    if alpha is not None:
+        _need(alpha, "alpha", torch.float32, 2)
+    else:
+        _need(head_decay, "head_decay", torch.float32, 1)
+        if head_decay.shape[0] != n_heads:
+            raise KernelError("gla_scan: one decay per head")
     _need(state, "state", torch.float32, 4)
     n, ld = projected.shape
     q_at, k_at, v_at, g_at = (int(c) for c in columns[:4])
-    if (alpha.shape != (n, n_heads * d) or norm_weight.shape[0] != e
-            or tuple(state.shape[1:]) != (n_heads, d, e) or out.shape != (n, n_heads * e)):
+    if ((alpha is not None and alpha.shape != (n, n_heads * d)) or tuple(state.shape[1:]) != (n_heads, d, e)
+            or (not raw_only and (norm_weight.shape[0] != e or out.shape != (n, n_heads * e)))):
         raise KernelError("gla_scan: shapes do not match the head counts")
     if max(q_at + n_heads * d, k_at + n_heads * d, v_at + n_heads * e, g_at + n_heads * e) > ld:
         raise KernelError("gla_scan: a column range lies outside the projection")
@@ -669,10 +690,11 @@ def gla_scan(projected, columns, alpha, q_scale, norm_weight, eps, state, seg_st
     lib = core()
     _check(lib, lib.qil_gla_scan(
         c_void_p(base + q_at * size), c_void_p(base + k_at * size), c_void_p(base + v_at * size),
-        c_void_p(base + g_at * size), _p(alpha), c_int(ld), c_float(q_scale), _p(norm_weight), c_float(eps), _p(state),
+        c_void_p(base + g_at * size), _p(alpha), _p(head_decay), c_int(1 if silu_inputs else 0),
+        c_int(1 if raw_only else 0), c_int(ld), c_float(q_scale), _p(norm_weight), c_float(eps), _p(state),
         _p(seg_start), _p(seg_len), _p(seg_row), c_int(n_segments), c_int(n), c_int(n_heads), c_int(d), c_int(e),
         _p(scratch), _p(out), c_int(mode), _p(decay_product), c_int(dtype_code(projected.dtype)),
-        c_int(dtype_code(norm_weight.dtype)), _stream()), "gla_scan")
+        c_int(dtype_code(norm_weight.dtype) if norm_weight is not None else F32), _stream()), "gla_scan")
     return out
 
 
@@ -704,6 +726,156 @@ def gla_norm_gate(scratch, projected, gate_column, norm_weight, eps, n_heads, e,
                                       c_int(e), _p(out), c_int(dtype_code(projected.dtype)),
                                       c_int(dtype_code(norm_weight.dtype)), _stream()), "gla_norm_gate")
     return out
+
+
+def lin_norm_gate_whole(scratch, projected, gate_column, norm_weight, eps, out):
+    """out [N, width] = ``scratch`` (float32 [N, width]) / sqrt(mean(scratch^2) + eps) * norm_weight * sigmoid(gate): one
+    norm over a token's whole row (all heads together); the gate is the ``width`` columns of ``projected`` from
+    ``gate_column`` on."""
+    _need(scratch, "scratch", torch.float32); _need(projected, "projected", ndim=2); _need(out, "out", projected.dtype, 2)
+    _need(norm_weight, "norm_weight", ndim=1)
+    n, width = out.shape
+    if projected.shape[0] != n or scratch.numel() < n * width or gate_column + width > projected.shape[1] \
+            or norm_weight.shape[0] != width:
+        raise KernelError("lin_norm_gate_whole: shapes do not fit together")
+    lib = core()
+    _check(lib, lib.qil_lin_norm_gate_whole(_p(scratch), c_void_p(projected.data_ptr() + gate_column * projected.element_size()),
+                                            c_int(projected.shape[1]), _p(norm_weight), c_float(eps), c_int(n), c_int(width),
+                                            _p(out), c_int(dtype_code(projected.dtype)),
+                                            c_int(dtype_code(norm_weight.dtype)), _stream()), "lin_norm_gate_whole")
+    return out
+
+
+def rms_join(x, a, weight, eps, mult=1.0, *, b=None, weight_a=None, weight_b=None, pre=0.5):
+    """x += mult * a / sqrt(mean(a^2) + eps) * weight, row by row in float32: a branch joins the stream ``x`` (float32
+    or bfloat16 [N, width], updated in place) through a norm on the branch.  With a second branch ``b``:
+    y = pre * (rms(a) * weight_a + rms(b) * weight_b), x += mult * rms(y) * weight."""
+    _need(x, "x", ndim=2); _need(a, "a", ndim=2); _need(weight, "weight", ndim=1)
+    if a.shape != x.shape or weight.shape[0] != x.shape[1]:
+        raise KernelError("rms_join: shapes differ")
+    if b is not None:
+        _need(b, "b", a.dtype, 2); _need(weight_a, "weight_a", weight.dtype, 1); _need(weight_b, "weight_b", weight.dtype, 1)
+        if b.shape != x.shape or weight_a.shape != weight.shape or weight_b.shape != weight.shape:
+            raise KernelError("rms_join: the second branch or its weights have another shape")
+    lib = core()
+    _check(lib, lib.qil_rms_join(_p(x), c_int(dtype_code(x.dtype)), _p(a), _p(weight_a), _p(b), _p(weight_b),
+                                 c_int(dtype_code(a.dtype)), _p(weight), c_int(dtype_code(weight.dtype)), c_int(x.shape[0]),
+                                 c_int(x.shape[1]), c_float(eps), c_float(pre), c_float(mult), _stream()), "rms_join")
+    return x
+
+
+def scale_inplace(x, factor):
+    """x *= factor for float32 ``x`` (logits)."""
+    _need(x, "x", torch.float32)
+    lib = core()
+    _check(lib, lib.qil_scale_inplace(_p(x), c_longlong(x.numel()), c_float(factor), _stream()), "scale_inplace")
+    return x
+
+
+ROTARY_HALVES, ROTARY_INTERLEAVED = 0, 1     # which dimensions pair up: i with i + dims / 2, or 2 i with 2 i + 1
+
+
+def _check_rotation(freq, rot_dims, layout, most, what):
+    if rot_dims:
+        _need(freq, "freq", torch.float32, 1)
+        if freq.shape[0] != rot_dims // 2:
+            raise KernelError(f"{what}: one frequency per rotated pair")
+    if rot_dims % 2 or not 0 <= rot_dims <= most or layout not in (ROTARY_HALVES, ROTARY_INTERLEAVED):
+        raise KernelError(f"{what}: {rot_dims} rotated dimensions of {most}, layout {layout}")
+
+
+def qk_rotate_store(proj, columns, q_out, kv_cache, q_norm_w, k_norm_w, eps, freq, rot_dims, layout, positions,
+                    token_row, block_table, n_q_heads, n_kv_heads, head_dim, v_dim, page_size):
+    """The tail of a q/k/v projection with rotation from frequencies (float32 angles position * freq[i]).
+
+    ``proj`` [N, width] holds q, k, v from the columns ``columns`` = (q, k, v) on.  With ``q_norm_w`` [Hq * d] and
+    ``k_norm_w`` [Hkv * d], q and k are first divided by their root mean square over the whole projection (all heads
+    at once) and multiplied by the weight.  Then the first ``rot_dims`` dimensions of every head are rotated
+    (``layout``: ``ROTARY_HALVES`` or ``ROTARY_INTERLEAVED``); queries go to ``q_out`` [N, Hq * d], keys and values
+    into the pages."""
+    _need(proj, "proj", ndim=2); _need(q_out, "q_out", proj.dtype, 2)
+    n, ld = proj.shape
+    q_at, k_at, v_at = (int(c) for c in columns)
+    if q_out.shape != (n, n_q_heads * head_dim) or max(q_at + n_q_heads * head_dim, k_at + n_kv_heads * head_dim,
+                                                       v_at + n_kv_heads * v_dim) > ld:
+        raise KernelError("qk_rotate_store: shapes do not match the head counts")
+    _check_rotation(freq, rot_dims, layout, head_dim, "qk_rotate_store")
+    norm_code = F32
+    if q_norm_w is not None:
+        _need(q_norm_w, "q_norm_w", ndim=1)
+        if n_kv_heads:
+            _need(k_norm_w, "k_norm_w", q_norm_w.dtype, 1)
+        if q_norm_w.shape[0] != n_q_heads * head_dim or (n_kv_heads and k_norm_w.shape[0] != n_kv_heads * head_dim):
+            raise KernelError("qk_rotate_store: the norm weights cover the whole projections")
+        norm_code = dtype_code(q_norm_w.dtype)
+    _need(positions, "positions", torch.int32, 1); _need(token_row, "token_row", torch.int32, 1)
+    num_pages = 0
+    if n_kv_heads:          # none: a layer that reads pages another layer wrote
+        check_pages(kv_cache, proj.dtype, n_kv_heads, page_size, head_dim, v_dim, "qk_rotate_store")
+        _need(block_table, "block_table", torch.int32, 2)
+        num_pages = kv_cache.shape[0]
+    lib = core()
+    _check(lib, lib.qil_qk_rotate_store(
+        _p(proj), c_int(ld), c_int(q_at), c_int(k_at), c_int(v_at), _p(q_out), _p(kv_cache if n_kv_heads else None),
+        _p(q_norm_w), _p(k_norm_w), c_int(norm_code), c_float(eps), _p(freq), c_int(rot_dims), c_int(layout),
+        _p(positions), _p(token_row), _p(block_table if n_kv_heads else None),
+        c_int(block_table.shape[1] if n_kv_heads else 0), c_int(n), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim),
+        c_int(v_dim), c_int(page_size), c_int(num_pages), c_int(dtype_code(proj.dtype)), _stream()),
+        "qk_rotate_store")
+    return q_out
+
+
+def latent_prepare(proj, q_column, kv_column, q_att, kv_cache, norm_w, eps, freq, rot_dims, layout, positions, token_row,
+                   block_table, n_heads, plain_dim, rot_dim, latent_dim, value_width, page_size):
+    """The tail of a latent attention's projection.  ``proj`` [N, width] holds the queries [H][plain_dim, rot_dim]
+    from ``q_column`` on and one row [latent_dim, rot_dim] per token from ``kv_column`` on.  The latent is normed
+    (root mean square, ``norm_w``), the shared key part and the queries' rotated parts are rotated; the token's page
+    row becomes key [latent, rotated part] and value [latent, zeros up to ``value_width``]; the rotated query parts
+    go to the last rot_dim columns of every head's row of ``q_att`` [N, H * (latent_dim + rot_dim)]."""
+    _need(proj, "proj", ndim=2); _need(q_att, "q_att", proj.dtype, 2); _need(norm_w, "norm_w", ndim=1)
+    n, ld = proj.shape
+    width = latent_dim + rot_dim
+    if q_att.shape != (n, n_heads * width) or norm_w.shape[0] != latent_dim \
+            or max(q_column + n_heads * (plain_dim + rot_dim), kv_column + width) > ld:
+        raise KernelError("latent_prepare: shapes do not fit together")
+    _check_rotation(freq, rot_dims, layout, rot_dim, "latent_prepare")
+    _need(positions, "positions", torch.int32, 1); _need(token_row, "token_row", torch.int32, 1)
+    check_pages(kv_cache, proj.dtype, 1, page_size, width, value_width, "latent_prepare")
+    _need(block_table, "block_table", torch.int32, 2)
+    lib = core()
+    _check(lib, lib.qil_latent_prepare(
+        _p(proj), c_int(ld), c_int(q_column), c_int(kv_column), _p(q_att), _p(kv_cache), _p(norm_w),
+        c_int(dtype_code(norm_w.dtype)), c_float(eps), _p(freq), c_int(rot_dims), c_int(layout), _p(positions),
+        _p(token_row), _p(block_table), c_int(block_table.shape[1]), c_int(n), c_int(n_heads), c_int(plain_dim),
+        c_int(rot_dim), c_int(latent_dim), c_int(value_width), c_int(page_size), c_int(kv_cache.shape[0]),
+        c_int(dtype_code(proj.dtype)), _stream()), "latent_prepare")
+    return q_att
+
+
+def head_product(x, x_column, x_head_stride, weight, y, y_column, y_head_stride, *, gate=None, gate_column=0):
+    """y[n, y_column + h * y_head_stride + j] = sum_i weight[h, j, i] * x[n, x_column + h * x_head_stride + i], times
+    sigmoid(gate[n, gate_column + h]) when ``gate`` is given: one small product per head over column ranges of the
+    row-major buffers ``x`` and ``y`` (float32 sums).  ``weight`` [H, out, in]."""
+    _need(x, "x", ndim=2); _need(y, "y", x.dtype, 2); _need(weight, "weight", ndim=3)
+    heads, n_out, n_in = weight.shape
+    n = x.shape[0]
+    if y.shape[0] != n or x_column + (heads - 1) * x_head_stride + n_in > x.shape[1] \
+            or y_column + (heads - 1) * y_head_stride + n_out > y.shape[1]:
+        raise KernelError("head_product: a column range lies outside its buffer")
+    gate_ptr, gate_row = c_void_p(0), 0
+    if gate is not None:
+        _need(gate, "gate", x.dtype, 2)
+        if gate.shape[0] != n or gate_column + heads > gate.shape[1]:
+            raise KernelError("head_product: the gate's columns lie outside its buffer")
+        gate_ptr, gate_row = c_void_p(gate.data_ptr() + gate_column * gate.element_size()), gate.shape[1]
+    size = x.element_size()
+    lib = core()
+    _check(lib, lib.qil_head_product(
+        c_void_p(x.data_ptr() + x_column * size), c_longlong(x.shape[1]), c_int(x_head_stride), _p(weight),
+        c_void_p(y.data_ptr() + y_column * size), c_longlong(y.shape[1]), c_int(y_head_stride), gate_ptr,
+        c_longlong(gate_row), c_int(n), c_int(heads), c_int(n_in), c_int(n_out), c_int(dtype_code(x.dtype)),
+        c_int(dtype_code(weight.dtype)), _stream()), "head_product")
+    return y
 
 
 def moe_route(x, router, bias, top, *, softmax_all=False, correction=None, weight_scale=1.0, gate_row=False):

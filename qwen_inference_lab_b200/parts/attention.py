@@ -22,7 +22,14 @@ q_p * (1 + coef * ln(floor((p + 1) / every) + 1))), and value heads of another s
                    score by distance: one row per distance below rows / 2, then rows that grow with the logarithm
                    of the distance up to ``farthest``, the last row for everything beyond (``distance_rows``)
 ``chunk``          position i sees the keys j <= i of its own chunk only: floor(i / chunk) = floor(j / chunk)
-``sink``           one is added to the softmax's denominator (a key of score zero without a value)
+``sink``           one is added to the softmax's denominator (a key of score zero without a value); ``"learned"``:
+                   exp(s_h) is added instead, s_h a learned score per query head (``names["sink"]``) that is not scaled
+
+A rotation whose angles the kernels compute from frequencies (``position`` a :class:`RotaryFrequencies`: either
+layout, on the first dimensions of a head only if so wished) and ``whole_qk_norm_eps`` (q and k are each divided by
+their root mean square over the whole projection, all heads at once, and multiplied by a weight per element
+``names["q_norm"]``, ``names["k_norm"]``, before the rotation) go with every option above but the per-head norms,
+the short convolution and the query temperature.
 """
 from __future__ import annotations
 
@@ -33,6 +40,7 @@ import torch
 from ..kernels import attention_mma, gemm_tc, ops
 from .base import KVCacheSpec, Mixer, Param, StateSpec, StepPlanner
 from .linear import Linear, StackedLinear
+from .rotary import RotaryFrequencies
 
 
 class PagedAttentionPlanner(StepPlanner):
@@ -81,7 +89,7 @@ class GroupedQueryAttention(Mixer):
                  qk_norm_eps=None, position=None, window=0, scale=None, reads_shared_cache=False,
                  v_head_dim=None, distance_slopes=None, q_temperature=None, out_bias=None,
                  suffixes=(".weight", ".bias"), conv_taps=0, conv_suffix=".conv", softcap=0.0, distance_bias=None,
-                 chunk=0, sink=False):
+                 chunk=0, sink=False, whole_qk_norm_eps=None, norm_suffix=".weight"):
         if n_q_heads % n_kv_heads:
             raise ValueError(f"{n_q_heads} query heads do not divide into {n_kv_heads} kv heads")
         self.hidden_size, self.head_dim = int(hidden_size), int(head_dim)
@@ -99,6 +107,16 @@ class GroupedQueryAttention(Mixer):
         if self.q_temperature is not None and self.q_temperature[1] < 1:
             raise ValueError("the query temperature's step must be a positive number of positions")
         self.conv_taps, self.softcap, self.chunk, self.sink = int(conv_taps), float(softcap or 0.0), int(chunk or 0), bool(sink)
+        self.learned_sink = sink == "learned"
+        self.whole_qk_norm_eps = None if whole_qk_norm_eps is None else float(whole_qk_norm_eps)
+        # the projection's tail is the kernel that norms over the whole projection and rotates by frequencies
+        self.frequency_tail = isinstance(position, RotaryFrequencies) or self.whole_qk_norm_eps is not None
+        if self.frequency_tail and (qk_norm_eps is not None or conv_taps or q_temperature is not None
+                                    or (position is not None and not isinstance(position, RotaryFrequencies))):
+            raise ValueError("rotation from frequencies and the norm over the whole projection go without per-head "
+                             "norms, a rotary table, a short convolution or a query temperature")
+        if isinstance(position, RotaryFrequencies) and position.rotary_dim > self.head_dim:
+            raise ValueError(f"{position.rotary_dim} rotated dimensions in heads of {self.head_dim}")
         if self.conv_taps < 0 or self.softcap < 0 or self.chunk < 0:
             raise ValueError("taps, softcap and chunk size cannot be negative")
         self.distance_bias = None if not distance_bias else (int(distance_bias[0]), int(distance_bias[1]))
@@ -110,7 +128,7 @@ class GroupedQueryAttention(Mixer):
                            or self.q_temperature is not None or self.conv_taps > 0 or self.modified_scores)
         if self.conv_taps and self.q_temperature is not None:
             raise ValueError("the short convolution goes without a query temperature")
-        if self.plain_tail and (qk_norm_eps is not None or position is not None):
+        if self.plain_tail and not self.frequency_tail and (qk_norm_eps is not None or position is not None):
             raise ValueError("distance slopes, query temperature and a value size of its own go without q/k norms and rotation")
         self._slopes = self._slopes_log2 = None
         pieces = [(names["q"], n_q_heads * head_dim)]
@@ -130,7 +148,18 @@ class GroupedQueryAttention(Mixer):
             distance_rows(self.distance_bias[0], self.distance_bias[1], 1)      # refuses constants that do not fit
             self.distance_table = Param((self.distance_bias[0], self.n_q_heads), std=0.5)
             self._extra[names["distance_bias"]] = self.distance_table
-        self._conv_w = self._bias_by_distance = self._options = None
+        self.sink_logits = None
+        if self.learned_sink:
+            self.sink_logits = Param((self.n_q_heads,), std=1.0)
+            self._extra[names["sink"]] = self.sink_logits
+        self.whole_q_norm = self.whole_k_norm = None
+        if self.whole_qk_norm_eps is not None:
+            self.whole_q_norm = Param((n_q_heads * head_dim,), init="norm", std=0.05)
+            self._extra[names["q_norm"] + norm_suffix] = self.whole_q_norm
+            if not self.reads_shared_cache:
+                self.whole_k_norm = Param((n_kv_heads * head_dim,), init="norm", std=0.05)
+                self._extra[names["k_norm"] + norm_suffix] = self.whole_k_norm
+        self._conv_w = self._bias_by_distance = self._options = self._sinks = None
         self.q_norm = self.k_norm = None
         self._norm_names = None
         if qk_norm_eps is not None:
@@ -170,7 +199,13 @@ class GroupedQueryAttention(Mixer):
                 count = max(1, min(count, self.chunk))
             index = torch.tensor(of_distance[:count], dtype=torch.long, device=self.distance_table.data.device)
             self._bias_by_distance = self.distance_table.data.float()[index].t().contiguous()
-        self._options = attention_mma.ScoreOptions(self.softcap, self._bias_by_distance, self.chunk, self.sink)
+        if self.sink_logits is not None:           # the softmax runs in float32 whatever the activations are
+            self._sinks = self.sink_logits.data.float().contiguous()
+        if self.whole_q_norm is not None and self.whole_k_norm is not None \
+                and self.whole_q_norm.data.dtype != self.whole_k_norm.data.dtype:
+            self.whole_q_norm.data, self.whole_k_norm.data = self.whole_q_norm.data.float(), self.whole_k_norm.data.float()
+        self._options = attention_mma.ScoreOptions(self.softcap, self._bias_by_distance, self.chunk, self.sink,
+                                                   sink_logits=self._sinks)
 
     def step_planners(self):
         return {**super().step_planners(), _PLANNER.key: _PLANNER}
@@ -191,14 +226,31 @@ class GroupedQueryAttention(Mixer):
 
     @property
     def takes_out_scale(self):
-        return self.plain_tail
+        return self.plain_tail or self.frequency_tail
 
-    def forward(self, ctx, x, cache, residual=None, norm=None, out_scale=None):
+    def forward(self, ctx, x, cache, residual=None, norm=None, out_scale=None, out_float32=False):
         """x [N, hidden] -> [N, hidden] (+ residual).  ``cache`` is a KVCacheView (with a short convolution: a
         pair of it and a StateView).  With ``norm`` x is the block's un-normed input and the first projection
         applies the norm."""
         n = x.shape[0]
         n_kv = 0 if self.reads_shared_cache else self.n_kv_heads
+        if self.frequency_tail:
+            qkv = self.qkv.forward(ctx, x, norm=norm)
+            q = ctx.empty((n, self.n_q_heads * self.head_dim))
+            q_width, k_width = self.n_q_heads * self.head_dim, n_kv * self.head_dim
+            rotation = self.position
+            ops.qk_rotate_store(qkv, (0, q_width, q_width + k_width), q, cache.pages,
+                                self.whole_q_norm.data if self.whole_q_norm is not None else None,
+                                self.whole_k_norm.data if self.whole_k_norm is not None else None,
+                                self.whole_qk_norm_eps or 0.0, rotation.freq if rotation is not None else None,
+                                rotation.rotary_dim if rotation is not None else 0,
+                                rotation.layout if rotation is not None else 0, ctx.positions, ctx.token_row,
+                                cache.block_table, self.n_q_heads, n_kv, self.head_dim, self.v_head_dim, cache.page_size)
+            attended = ctx.empty((n, self.n_q_heads * self.v_head_dim))
+            self._attend(ctx, q, cache, attended)
+            return self.out.forward(ctx, attended, residual=residual, out_scale=out_scale, out_float32=out_float32)
+        if out_float32:
+            raise ValueError("a float32 result is given by the layers that rotate by frequencies only")
         if self.plain_tail:
             qkv = self.qkv.forward(ctx, x, norm=norm)
             q = ctx.empty((n, self.n_q_heads * self.head_dim))
@@ -265,7 +317,7 @@ class GroupedQueryAttention(Mixer):
                                   self.n_q_heads, self.n_kv_heads, self.head_dim, cache.page_size,
                                   self.window, self.scale, v_dim=self.v_head_dim, slopes=self._slopes,
                                   softcap=self.softcap, distance_bias=self._bias_by_distance, chunk=self.chunk,
-                                  sink=self.sink)
+                                  sink=self.sink, sink_logits=self._sinks)
             return
         if q.dtype == torch.bfloat16 and self.v_head_dim == self.head_dim \
                 and attention_mma.supports(self.head_dim, self.n_q_heads, self.n_kv_heads):

@@ -10,6 +10,9 @@ Two options for other designs.  A learned scale per feature on each branch befor
 (``scales``: the two tensors' names): x <- x + s1 * mixer(norm1 x), x <- x + s2 * ff(norm2 x); a part that sets
 ``takes_out_scale`` applies the scale in its last kernel, the others' results are scaled and added by a kernel
 of the block's.  And parts that run on the stream after the feed-forward (``after``: each ``forward(ctx, x) -> x``).
+
+:class:`PostNormBlock` is the other arrangement: the sublayers read the stream itself and the norm sits on each
+sublayer's output, x <- x + m * norm1(mixer(x)), x <- x + m * norm2(ff(x)) with a fixed multiplier m.
 """
 from __future__ import annotations
 
@@ -86,3 +89,44 @@ class PreNormBlock(Part):
         if getattr(self.feed_forward, "takes_norm", False):
             return self.feed_forward.forward(ctx, x, residual=x, norm=self.ff_norm)
         return self.feed_forward.forward(ctx, self.ff_norm.forward(ctx, x), residual=x)
+
+
+class PostNormBlock(Part):
+    """x <- x + mult * rms(mixer(x); w1), then x <- x + mult * rms(ff(x); w2): the sublayers read the residual
+    stream itself (cast to the activation dtype when the stream is float32 under bfloat16 activations) and their
+    output is normed (root mean square over the width, a weight per feature, float32) before it joins the stream.
+    The norm, the multiplier and the sum are one kernel (``kernels.ops.rms_join``).  A mixer that sets
+    ``joins_stream`` is handed the stream, the weight and the multiplier and does the join itself (two mixers side
+    by side fold their own output norms into that kernel).  ``feed_forward`` may be None; the second norm's weight
+    is then optional.  names: (first norm's weight, second norm's weight)."""
+
+    def __init__(self, width, eps, mult, mixer, feed_forward, *, names, norm_suffix=".weight"):
+        self.width, self.eps, self.mult = int(width), float(eps), float(mult)
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm = Param((width,), init="norm", std=0.05)
+        self.ff_norm = Param((width,), init="norm", std=0.05, optional=feed_forward is None)
+        self._names = {names[0] + norm_suffix: self.mixer_norm, names[1] + norm_suffix: self.ff_norm}
+        self.graph_safe = True
+
+    def named_params(self):
+        return dict(self._names)
+
+    def children(self):
+        return [part for part in (self.mixer, self.feed_forward) if part is not None]
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, ctx, x, cache):
+        """x [N, width] is the residual stream; updated in place and returned."""
+        rows = x if x.dtype == ctx.dtype else ops.cast(x, ctx.dtype)
+        if getattr(self.mixer, "joins_stream", False):
+            x = self.mixer.forward(ctx, rows, cache, stream=x, norm_weight=self.mixer_norm.data, mult=self.mult)
+        else:
+            branch = self.mixer.forward(ctx, rows, cache, out_float32=True)
+            x = ops.rms_join(x, branch, self.mixer_norm.data, self.eps, self.mult)
+        if self.feed_forward is None:
+            return x
+        rows = x if x.dtype == ctx.dtype else ops.cast(x, ctx.dtype)
+        branch = self.feed_forward.forward(ctx, rows, out_float32=True)
+        return ops.rms_join(x, branch, self.ff_norm.data, self.eps, self.mult)

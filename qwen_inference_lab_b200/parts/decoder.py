@@ -49,10 +49,13 @@ class TokenEmbedding(Part):
 class DecoderModel(Part):
     graph_safe = True      # the model itself only walks its parts; they decide
 
-    def __init__(self, *, config, embedding, layers, order, final_norm, head, max_positions, stream_dtype=None):
+    def __init__(self, *, config, embedding, layers, order, final_norm, head, max_positions, stream_dtype=None,
+                 logit_scale=1.0):
         """``stream_dtype``: the dtype of the residual stream where it is not the activations' (float32 for
-        designs that sum their residuals in 32 bits while their products run in bfloat16)."""
+        designs that sum their residuals in 32 bits while their products run in bfloat16).
+        ``logit_scale``: what the head's float32 products are multiplied by."""
         self.config = config
+        self.logit_scale = float(logit_scale)
         self.stream_dtype = stream_dtype
         self.embedding, self.layers, self.final_norm, self.head = embedding, list(layers), final_norm, head
         self.order = [call if isinstance(call, LayerCall) else LayerCall(*call) for call in order]
@@ -101,4 +104,5 @@ class DecoderModel(Part):
         if logit_rows is None or logit_rows.shape[0] == 0:
             return None
         normed = self.final_norm.forward(ctx, x, rows=logit_rows)
-        return self.head.forward(ctx, normed, out_float32=True)
+        logits = self.head.forward(ctx, normed, out_float32=True)
+        return ops.scale_inplace(logits, self.logit_scale) if self.logit_scale != 1.0 else logits

@@ -52,13 +52,14 @@ class GatedMLP(FeedForward):
 
     takes_norm = True
 
-    def forward(self, ctx, x, residual=None, norm=None):
+    def forward(self, ctx, x, residual=None, norm=None, out_float32=False):
         """With ``norm`` x is the block's un-normed input; a decode step's few rows get the norm inside
-        the gate/up kernel, longer steps a norm kernel of their own."""
-        if self.activation != "silu" or self.bias:
+        the gate/up kernel, longer steps a norm kernel of their own.  ``out_float32``: the down product's float32
+        sums are returned as they are (for a block that norms the branch before it joins the stream)."""
+        if self.activation != "silu" or self.bias or out_float32:
             gate_up = self.gate_up.forward(ctx, x, norm=norm)
-            hidden = ops.gated_activation(gate_up, self.activation, limit=self.limit, alpha=self.alpha)
-            return self.down.forward(ctx, hidden, residual=residual)
+            hidden = ops.gated_activation(gate_up, self.activation, limit=self.limit, alpha=self.alpha, pairs8=self.pairs8)
+            return self.down.forward(ctx, hidden, residual=residual, out_float32=out_float32)
         rms = norm.as_rms() if norm is not None else None
         if self.pairs8 and ops.small_m_ok(x, self.gate_up._w) and rms is not None and rms[0].dtype == torch.bfloat16:
             hidden = ops.gemm_small_m(x, self.gate_up._w, silu_pairs=True, norm_weight=rms[0], norm_eps=rms[1])

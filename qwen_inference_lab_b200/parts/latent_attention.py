@@ -1,0 +1,104 @@
+"""Latent attention: keys and values of all heads grow out of one small latent per token, which is all the cache keeps.
+
+Per token, with H heads, d plain and r rotated query/key dimensions per head, e value dimensions and a latent of c:
+
+    q = Wq h                          [H][d plain, r rotated]
+    (l, s) = Wdkv h                   c + r rows;  z = l / sqrt(mean(l^2) + eps) * w  (float32);  s is one rotated key
+                                      part shared by all heads
+    key of head a   = [Wuk_a z, rot(s)]      value of head a = Wuv_a z
+    score           = (q_plain . Wuk_a z + rot(q_rot) . rot(s)) * scale,  softmax inside a sliding window
+    y = Wo concat_a( sigmoid(Wg h)_a * sum_j p_j Wuv_a z_j )
+
+Only z and rot(s) are cached: the products with Wuk and Wuv are moved to the query's side.  q_plain . (Wuk_a z) =
+(Wuk_a^T q_plain) . z, so the query of head a becomes [Wuk_a^T q_plain, rot(q_rot)] of c + r numbers, every head reads
+the same key row [z, rot(s)] (attention with one key/value head), the weighted sum runs over the z_j, and Wuv_a is
+applied once to that sum.  Kernels: the stacked projection (q, dkv, g); ``ops.latent_prepare`` (norm of the latent,
+the rotations, the page write); ``ops.head_product`` (the query through Wuk^T); the engine's paged attention with a
+window; ``ops.head_product`` again (the sum through Wuv, times the gate); the output product.
+
+A page holds the token's key row [z, rot(s)] and its value row.  Where c + r is a head size the tensor-core
+attention takes (a multiple of 16 up to 256), the value row is z followed by r zeros, so that keys and values
+have one size as that kernel wants; otherwise the value row is z alone and the float32 kernel runs.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import attention_mma, ops
+from .attention import _PLANNER
+from .base import KVCacheSpec, Mixer, Param
+from .linear import Linear, StackedLinear
+from .rotary import RotaryFrequencies
+
+
+class LatentAttention(Mixer):
+    """names: dict with keys q, dkv, dkv_norm, uk, uv, g, o (tensor names; ``suffixes`` are appended to the
+    projections', ``norm_suffix`` to the norm's).  ``position``: a :class:`RotaryFrequencies` over the rotated part."""
+    graph_safe = True
+
+    def __init__(self, hidden_size, n_heads, plain_dim, rot_dim, value_dim, latent_dim, *, scale, window, position,
+                 norm_eps, names, suffixes=(".weight", ".bias"), norm_suffix=".weight"):
+        self.hidden_size, self.n_heads = int(hidden_size), int(n_heads)
+        self.plain_dim, self.rot_dim, self.value_dim, self.latent_dim = int(plain_dim), int(rot_dim), int(value_dim), int(latent_dim)
+        self.scale, self.window, self.norm_eps = float(scale), int(window or 0), float(norm_eps)
+        if not isinstance(position, RotaryFrequencies) or position.rotary_dim > self.rot_dim:
+            raise ValueError("latent attention rotates by frequencies, over at most its rotated dimensions")
+        self.position = position
+        self.key_width = self.latent_dim + self.rot_dim
+        # the value row's width: see the module's text
+        self.value_width = self.key_width if attention_mma.supports(self.key_width, 1, 1) else self.latent_dim
+        q_width = self.n_heads * (self.plain_dim + self.rot_dim)
+        self.projection = StackedLinear(hidden_size, [(names["q"], q_width), (names["dkv"], self.key_width),
+                                                      (names["g"], self.n_heads)], suffixes=suffixes)
+        self.columns = (0, q_width, q_width + self.key_width)
+        self.latent_norm = Param((self.latent_dim,), init="norm", std=0.05)
+        self.key_up = Param((self.n_heads * self.plain_dim, self.latent_dim))
+        self.value_up = Param((self.n_heads * self.value_dim, self.latent_dim))
+        self._names = {names["dkv_norm"] + norm_suffix: self.latent_norm, names["uk"] + suffixes[0]: self.key_up,
+                       names["uv"] + suffixes[0]: self.value_up}
+        self.out = Linear(self.n_heads * self.value_dim, hidden_size, name=names["o"], suffixes=suffixes)
+        self._query_fold = self._value_unfold = None
+
+    def named_params(self):
+        return dict(self._names)
+
+    def children(self):
+        return [self.projection, self.out, self.position]
+
+    def finalize(self, device, dtype):
+        super().finalize(device, dtype)
+        common = self.projection._weight().dtype
+        # per head: the query's plain part through Wuk_a^T [c, d]; the weighted sum of latents through Wuv_a [e, c]
+        up = self.key_up.data.to(common).view(self.n_heads, self.plain_dim, self.latent_dim)
+        self._query_fold = up.transpose(1, 2).contiguous()
+        self._value_unfold = self.value_up.data.to(common).view(self.n_heads, self.value_dim, self.latent_dim).contiguous()
+        self.key_up.data = self.value_up.data = None
+        self.latent_norm.data = self.latent_norm.data.to(common).contiguous()
+
+    def step_planners(self):
+        return {**super().step_planners(), _PLANNER.key: _PLANNER}
+
+    def cache_spec(self):
+        return KVCacheSpec(1, self.key_width, self.window, self.value_width if self.value_width != self.key_width else 0)
+
+    def forward(self, ctx, x, cache, residual=None, out_float32=False):
+        """x [N, hidden] -> [N, hidden] (+ residual); ``cache`` is a KVCacheView of rows [latent, rotated key part]."""
+        n, heads, width = x.shape[0], self.n_heads, self.key_width
+        projected = self.projection.forward(ctx, x)
+        queries = ctx.empty((n, heads * width))
+        rotation = self.position
+        ops.latent_prepare(projected, self.columns[0], self.columns[1], queries, cache.pages, self.latent_norm.data,
+                           self.norm_eps, rotation.freq, rotation.rotary_dim, rotation.layout, ctx.positions, ctx.token_row,
+                           cache.block_table, heads, self.plain_dim, self.rot_dim, self.latent_dim, self.value_width,
+                           cache.page_size)
+        ops.head_product(projected, self.columns[0], self.plain_dim + self.rot_dim, self._query_fold, queries, 0, width)
+        attended = ctx.empty((n, heads * self.value_width))
+        if queries.dtype == torch.bfloat16 and self.value_width == width:
+            attention_mma.attend(ctx, queries, cache, attended, heads, 1, width, self.window, self.scale)
+        else:
+            ops.attention_generic(queries, cache.pages, attended, ctx.positions, ctx.token_row, cache.block_table, heads, 1,
+                                  width, cache.page_size, self.window, self.scale, v_dim=self.value_width)
+        mixed = ctx.empty((n, heads * self.value_dim))
+        ops.head_product(attended, 0, self.value_width, self._value_unfold, mixed, 0, self.value_dim,
+                         gate=projected, gate_column=self.columns[2])
+        return self.out.forward(ctx, mixed, residual=residual, out_float32=out_float32)

@@ -132,3 +132,77 @@ class GatedLinearAttention(Mixer):
             ops.gla_norm_gate(scratch, projected, self.columns[3], self.norm_weight.data, self.norm_eps, self.n_heads,
                               self.value_dim, mixed)
         return mixed
+
+
+class DecayLinearAttention(Mixer):
+    """Linear attention with one fixed decay per head (a state matrix per head and request, float32):
+
+        q_t = silu(Wq x_t), k_t = silu(Wk x_t)  [H][d];   v_t = silu(Wv x_t)  [H][e]
+        S_t = decay_h S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t                   S_0 = 0
+        y_t = Wo ( o_t / sqrt(mean(o_t^2) + eps) * w  *  sigmoid(Wg x_t) )     one norm over all heads' H * e values
+
+    q, k, v and the gate are one stacked product.  The recurrence is the scan of :class:`GatedLinearAttention`
+    (``kernels.ops.gla_scan``) with a decay per head in place of decays per token and the activation applied as
+    q, k and v are read; it shares that mixer's step plan, so short segments run token by token and long ones as
+    chunks with a carry.  The scan leaves the un-normed outputs in float32; ``kernels.ops.lin_norm_gate_whole``
+    norms a token's whole row and gates it.
+
+    names: dict with keys q, k, v, g, o (projection names) and norm (the output norm's weight)."""
+    graph_safe = True
+
+    def __init__(self, hidden_size, n_heads, key_dim, value_dim, decay, *, norm_eps, names,
+                 suffixes=(".weight", ".bias"), norm_suffix=".weight"):
+        self.hidden_size, self.n_heads = int(hidden_size), int(n_heads)
+        self.key_dim, self.value_dim, self.norm_eps = int(key_dim), int(value_dim), float(norm_eps)
+        self.decay = [float(v) for v in decay]
+        if len(self.decay) != self.n_heads or any(not 0.0 <= v <= 1.0 for v in self.decay):
+            raise ValueError("one decay in [0, 1] per head")
+        kw, vw = self.n_heads * self.key_dim, self.n_heads * self.value_dim
+        self.projection = StackedLinear(hidden_size, [(names["q"], kw), (names["k"], kw), (names["v"], vw), (names["g"], vw)],
+                                        suffixes=suffixes)
+        self.columns = (0, kw, 2 * kw, 2 * kw + vw)
+        self.norm_weight = Param((vw,), init="norm", std=0.05)
+        self._names = {names["norm"] + norm_suffix: self.norm_weight}
+        self.out = Linear(vw, hidden_size, name=names["o"], suffixes=suffixes)
+        self._decay = None
+
+    def named_params(self):
+        return dict(self._names)
+
+    def children(self):
+        return [self.projection, self.out]
+
+    def finalize(self, device, dtype):
+        super().finalize(device, dtype)
+        self.norm_weight.data = self.norm_weight.data.to(self.projection._weight().dtype).contiguous()
+        self._decay = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(device)
+        ops.gla_scan_needs_scratch(self.key_dim, self.value_dim)       # refuses key sizes the scan cannot hold
+
+    def cache_spec(self):
+        return StateSpec((self.n_heads, self.key_dim, self.value_dim), torch.float32)
+
+    def step_planners(self):
+        return {**super().step_planners(), _PLANNER.key: _PLANNER}
+
+    def forward(self, ctx, x, cache, residual=None, out_float32=False):
+        """x [N, hidden] -> [N, hidden] (+ residual); ``cache`` is a StateView with one slot per request row."""
+        n, heads, d, e = x.shape[0], self.n_heads, self.key_dim, self.value_dim
+        projected = self.projection.forward(ctx, x)
+        plan = ctx.plans[_PLANNER.key]
+        raw = ctx.empty((n, heads * e), dtype=torch.float32)
+        common = (projected, self.columns, None, 1.0, None, self.norm_eps)
+        options = dict(head_decay=self._decay, silu_inputs=True, raw_only=True)
+        n_short, n_chunks = plan.count["short_start"], plan.count["chunk_start"]
+        if n_short:
+            ops.gla_scan(*common, cache.slots, plan.array["short_start"], plan.array["short_len"], plan.array["short_row"],
+                         n_short, heads, d, e, None, scratch=raw, **options)
+        if n_chunks:
+            chunk = (plan.array["chunk_start"], plan.array["chunk_len"], plan.array["chunk_index"], n_chunks)
+            states = ctx.empty((n_chunks, heads, d, e), dtype=torch.float32)
+            decays = ctx.empty((n_chunks, heads, d), dtype=torch.float32)
+            ops.gla_scan(*common, states, *chunk, heads, d, e, None, mode=ops.GLA_OWN_STATE, decay_product=decays, **options)
+            ops.gla_carry(states, decays, cache.slots, plan.array["carry"], plan.count["carry"] // 3)
+            ops.gla_scan(*common, states, *chunk, heads, d, e, None, scratch=raw, mode=ops.GLA_FROM_STATE, **options)
+        mixed = ctx.empty((n, heads * e))
+        ops.lin_norm_gate_whole(raw, projected, self.columns[3], self.norm_weight.data, self.norm_eps, mixed)
+        return self.out.forward(ctx, mixed, residual=residual, out_float32=out_float32)

@@ -35,3 +35,25 @@ class RotaryEmbedding(PositionEncoding):
 
     def finalize(self, device, dtype):
         self.table = rotary_table(self.rotary_dim, self.theta, self.max_positions, dtype).to(device)
+
+
+class RotaryFrequencies(PositionEncoding):
+    """Rotation whose angles the kernels compute themselves, in float32: pair i at position p turns by
+    ``float(p) * freq[i]`` with ``freq[i] = base^(-2 i / dims)``, i < dims / 2.  No table: a request may be as long
+    as the cache allows.  ``layout`` says which of the ``dims`` rotated dimensions of a vector pair up:
+    ``"halves"`` (i with i + dims / 2) or ``"interleaved"`` (2 i with 2 i + 1); dimensions from ``dims`` on pass
+    unchanged.  The frequencies are made on the host in float64 and rounded once to float32."""
+    graph_safe = True
+    LAYOUTS = {"halves": 0, "interleaved": 1}
+
+    def __init__(self, dims, base, layout="halves"):
+        if dims % 2 or dims <= 0:
+            raise ValueError(f"the number of rotated dimensions must be positive and even, got {dims}")
+        if layout not in self.LAYOUTS:
+            raise ValueError(f"unknown rotary layout {layout!r} (known: {sorted(self.LAYOUTS)})")
+        self.rotary_dim, self.base, self.layout = int(dims), float(base), self.LAYOUTS[layout]
+        self.freq = None
+
+    def finalize(self, device, dtype):
+        values = [self.base ** (-2.0 * i / self.rotary_dim) for i in range(self.rotary_dim // 2)]
+        self.freq = torch.tensor(values, dtype=torch.float64).to(torch.float32).to(device)
