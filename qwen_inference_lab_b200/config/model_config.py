@@ -319,7 +319,7 @@ class LarolornConfig:
     ``parallel`` one: ``left`` a grouped attention (``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``rot``,
     ``mask.size`` the chunk) beside ``right`` a linear attention with a fixed decay per head (``heads``, ``dim``,
     ``vdim``, ``decay``); and a feed-forward (``mlp``: ``dense`` with ``ff`` and ``limit``, or null).
-    ``weights_of: j`` names the earlier layer whose tensors the layer runs with (cache and state stay its own).
+    ``weights_of: j`` names the layer whose tensors the layer runs with (cache and state stay its own).
     The configuration is kept as the dictionary it came in; this class checks it and answers the few questions
     the engine asks.  ``max_positions`` (not a key of the design; 2**20 unless given) only bounds a request.
     """
@@ -379,8 +379,9 @@ class LarolornConfig:
                     raise ConfigError(f"{where}.mlp needs a positive ff and limit")
             source = layer.get("weights_of")
             if source is not None:
-                if type(source) is not int or not 0 <= source < index or layers[source].get("weights_of") is not None:
-                    raise ConfigError(f"{where}.weights_of must name an earlier layer that has tensors of its own")
+                if type(source) is not int or not 0 <= source < len(layers) or source == index \
+                        or layers[source].get("weights_of") is not None:
+                    raise ConfigError(f"{where}.weights_of must name another layer that has tensors of its own")
                 theirs = layers[source]
                 if any(theirs.get(k) != layer.get(k) for k in ("type", "mixer", "mlp")):
                     raise ConfigError(f"{where} and layers[{source}] share weights but differ in type, mixer or mlp")

@@ -64,18 +64,17 @@ def _feed_forward(width, mlp, prefix):
 
 def build_larolorn(config: LarolornConfig) -> DecoderModel:
     width, eps = config.width, config.eps
-    layers, order, block_of = [], [], {}
+    layers, block_of = [], {}
     for i, layer in enumerate(config.layers):
-        source = layer.get("weights_of")
-        if source is None:
+        if layer.get("weights_of") is None:
             prefix = f"l{i}."
             build = _latent if layer["type"] == "latent_attention" else _parallel
             block_of[i] = len(layers)
             layers.append(PostNormBlock(width, eps, config.residual_mult, build(width, layer["mixer"], prefix + "mix.", eps),
                                         _feed_forward(width, layer.get("mlp"), prefix + "mlp."),
                                         names=(prefix + "norm1", prefix + "norm2"), norm_suffix=""))
-            source = i
-        order.append(LayerCall(block_of[source]))
+    order = [LayerCall(block_of[i if layer.get("weights_of") is None else layer["weights_of"]])
+             for i, layer in enumerate(config.layers)]
     return DecoderModel(config=config, embedding=TokenEmbedding(config.vocab_size, width, name="embed", suffix=""),
                         layers=layers, order=order,
                         final_norm=ExactRMSNorm(width, eps, name="final.norm", suffix=""),

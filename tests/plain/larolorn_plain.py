@@ -194,7 +194,8 @@ def forward(config, w, tokens, dtype=torch.float64, low=None, return_layers=Fals
     x = w["embed"][tokens].to(dtype)
     after = []
     for i, layer in enumerate(config["layers"]):
-        p = f"l{layer.get('weights_of', i)}."
+        source = layer.get("weights_of")
+        p = f"l{i if source is None else source}."
         m = layer["mixer"]
         if layer["type"] == "latent_attention":
             y = latent_attention_mixer(x, w, p + "mix.", m, eps, low)
