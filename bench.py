@@ -829,6 +829,266 @@ def run_debisun(args):
 
 
 # --------------------------------------------------------------------------- the reference
+# --------------------------------------------------------------------------- Larolorn beside Virulix
+def _larolorn_sizes(width, heads, kv_heads, dim, rank, rot, lin_heads, lin_dim, lin_vdim, ff, span, vocab):
+    """Eight layers, latent attention and side-by-side mixers in turn; the third runs with the first one's tensors."""
+    latent = dict(heads=heads, dim=dim, rot_dim=rot, vdim=dim, kv_rank=rank, scale=(dim + rot) ** -0.5,
+                  rot=dict(base=10000.0, dims=rot), mask=dict(size=span))
+    left = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, rot=dict(base=500000.0, dims=dim),
+                mask=dict(size=span))
+    right = dict(heads=lin_heads, dim=lin_dim, vdim=lin_vdim, decay=[1.0 - 2.0 ** -(2 + i % 8) for i in range(lin_heads)])
+    mlp = dict(kind="dense", ff=ff, limit=7.0)
+    one = dict(type="latent_attention", mixer=latent, mlp=mlp)
+    two = dict(type="parallel", mixer=dict(left=left, right=right), mlp=mlp)
+    layers = [one, two, dict(one, weights_of=0), two, one, two, one, two]
+    return dict(architecture="Larolorn", vocab=vocab, width=width, norm=dict(eps=1e-6), residual_mult=0.5, logit_scale=0.25,
+                layers=layers)
+
+
+def _virulix_beside_larolorn(width, heads, kv_heads, dim, lin_heads, lin_dim, lin_vdim, ff, vocab, **_):
+    """Virulix of equal width, heads, layer count, feed-forward size and vocabulary: attention and gated linear
+    attention in turn, dense feed-forwards throughout."""
+    attention = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, q_temp=dict(coef=0.1, every=256))
+    gla = dict(heads=lin_heads, dim=lin_dim, vdim=lin_vdim, tau=16.0, rank=16)
+    mlp = dict(kind="dense", ff=ff)
+    layers = [dict(type=kind, mixer=mixer, mlp=mlp) for kind, mixer in (("attention", attention), ("gla", gla)) * 4]
+    return dict(architecture="Virulix", vocab=vocab, width=width, norm=dict(eps=1e-6), layers=layers)
+
+
+LAROLORN_SHAPES = {
+    "2048": dict(width=2048, heads=16, kv_heads=4, dim=128, rank=192, rot=64, lin_heads=8, lin_dim=128, lin_vdim=128, ff=6144,
+                 span=1024, vocab=32768),
+    "4096": dict(width=4096, heads=32, kv_heads=8, dim=128, rank=192, rot=64, lin_heads=16, lin_dim=128, lin_vdim=128, ff=12288,
+                 span=1024, vocab=32768),
+}
+
+
+class _PartKernels:
+    """Times one kernel (or a few) of a part inside the step function, on a whole prompt and on a step of single tokens
+    behind ``context`` cached positions, an L2 flush before every step: rows of (name, ms, fraction, of what)."""
+
+    def __init__(self, torch, pk, tokens_n, batch, context, flush):
+        self.torch, self.tokens_n, self.batch, self.context, self.flush = torch, tokens_n, batch, context, flush
+        self.tflops, self.gbs = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+        self.rows, self._marks = [], []
+
+    def timed(self, fn):
+        torch = self.torch
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out = fn()
+        stop.record()
+        self._marks.append((start, stop))
+        return out
+
+    def _median(self, skip):
+        self.torch.cuda.synchronize()
+        values = [a.elapsed_time(b) for a, b in self._marks[skip:]]
+        self._marks = []
+        return statistics.median(values)
+
+    def measure(self, name, part, hidden, kernel_of, prompt_work, decode_bytes, prompt_of=None):
+        """``kernel_of(ctx, x, view)`` runs the kernel under ``self.timed``.  ``prompt_work``: (FLOPs, None) for a kernel
+        bound by arithmetic, (None, bytes) for one bound by memory; ``prompt_of``: (peak in FLOP/s, its name) where
+        the bound is not the bfloat16 tensor peak."""
+        from qwen_inference_lab_b200.cache import CacheManager
+        from qwen_inference_lab_b200.engine import StepEntry, StepRunner
+        from tests.harness import OnePartModel
+        torch, tokens_n, batch, context = self.torch, self.tokens_n, self.batch, self.context
+        shell = OnePartModel(part, hidden, torch.bfloat16, kernel_of)
+        shell.inputs = torch.randn(4096, hidden, device="cuda").to(torch.bfloat16)
+        pages = (batch + 1) * ((max(tokens_n, context) + PAGE_SIZE) // PAGE_SIZE + 2)
+        cache = CacheManager(shell.cache_specs(), num_pages=pages, page_size=PAGE_SIZE, max_requests=batch + 1,
+                             max_context=pages * PAGE_SIZE, dtype=torch.bfloat16, device="cuda")
+        for g in cache.kv_groups:
+            g.storage.normal_(0.0, 0.5)
+        runner = StepRunner(shell, cache, max_step_tokens=tokens_n, use_graphs=False)
+        ids = [i % 4096 for i in range(tokens_n)]
+        for i in range(8):
+            self.flush.zero_()
+            cache.admit("p")
+            runner.run([StepEntry("p", ids, [])])
+            cache.release("p")
+            shell.outputs.clear()
+        ms = self._median(3)
+        flops, moved = prompt_work
+        if flops is not None:
+            peak, of = prompt_of or (self.tflops, "of the bf16 peak")
+            self.rows.append((f"{name} prompt {tokens_n}", ms, flops / (ms * 1e-3) / peak, of))
+        else:
+            self.rows.append((f"{name} prompt {tokens_n}", ms, moved / (ms * 1e-3) / self.gbs, "of the copy bandwidth"))
+        for rid in range(batch):
+            cache.admit(rid)
+            cache.ensure(rid, context)
+            cache.advance(rid, context)
+        for i in range(12):
+            self.flush.zero_()
+            runner.run([StepEntry(rid, [rid], []) for rid in range(batch)])
+            shell.outputs.clear()
+        ms = self._median(4)
+        self.rows.append((f"{name} decode b{batch} c{context}", ms, decode_bytes / (ms * 1e-3) / self.gbs, "of the copy bandwidth"))
+
+
+def _larolorn_kernels(torch, larolorn, virulix, sizes, pk, tokens_n, batch, context, flush):
+    """The kernels of Larolorn's mechanisms alone, each beside the like kernel of Virulix, with what the roofline allows."""
+    from qwen_inference_lab_b200.kernels import attention_mma, ops
+    bench = _PartKernels(torch, pk, tokens_n, batch, context, flush)
+    H, G, d, W = sizes["heads"], sizes["kv_heads"], sizes["dim"], sizes["width"]
+    span = sizes["span"]
+    latent = next(l.mixer for l in larolorn.layers if hasattr(l.mixer, "latent_dim"))
+    pair = next(l.mixer for l in larolorn.layers if hasattr(l.mixer, "left"))
+    theirs = next(l.mixer for l in virulix.layers if hasattr(l.mixer, "plain_tail"))
+    their_gla = next(l.mixer for l in virulix.layers if hasattr(l.mixer, "decay_rank"))
+    pairs_window = sum(min(i, span - 1) + 1 for i in range(tokens_n))             # (query, key) pairs of a prompt
+    pairs_chunk = sum(i % span + 1 for i in range(tokens_n))
+    pairs_all = tokens_n * (tokens_n + 1) // 2
+
+    # ---- attention itself
+    row = latent.key_width
+    def latent_attention(ctx, x, view):
+        q = x[:, :H * row].contiguous()
+        return bench.timed(lambda: latent.attend(ctx, q, view))
+    bench.measure(f"larolorn latent attention (one key row of {row} for {H} heads, window)", latent, H * row, latent_attention,
+                  (4.0 * H * row * pairs_window, None), batch * min(context + 1, span) * 2 * row * 2)
+    def grouped_attention(mixer):
+        def kernel(ctx, x, view):
+            q = x[:, :H * d].contiguous()
+            out = torch.empty_like(q)
+            view = view[0] if isinstance(view, tuple) else view
+            bench.timed(lambda: mixer._attend(ctx, q, view, out))
+            return out
+        return kernel
+    bench.measure("larolorn chunked attention (learned sinks)", pair.left, H * d, grouped_attention(pair.left),
+                  (4.0 * H * d * pairs_chunk, None), batch * (context % span + 1) * 2 * G * d * 2)
+    bench.measure("virulix attention (distance slopes)", theirs, H * d, grouped_attention(theirs),
+                  (4.0 * H * d * pairs_all, None), batch * (context + 1) * 2 * G * d * 2)
+
+    # ---- what stands between the projection and the attention
+    channels = (H + 2 * G) * d
+    moved = lambda n, width: 2 * n * width * 2          # every row read once and written once
+    left = pair.left
+    def rotate_store(ctx, x, view):
+        qkv = x[:, :channels].contiguous()
+        q = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)
+        bench.timed(lambda: ops.qk_rotate_store(qkv, (0, H * d, (H + G) * d), q, view.pages, left.whole_q_norm.data,
+                                                left.whole_k_norm.data, left.whole_qk_norm_eps, left.position.freq,
+                                                left.position.rotary_dim, left.position.layout, ctx.positions, ctx.token_row,
+                                                view.block_table, H, G, d, d, view.page_size))
+        return q
+    def plain_store(ctx, x, view):
+        qkv = x[:, :channels].contiguous()
+        q = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)
+        bench.timed(lambda: ops.qkv_store(qkv, q, view.pages, ctx.positions, ctx.token_row, view.block_table, H, G, d, d,
+                                          view.page_size, 0.1, 256))
+        return q
+    bench.measure("larolorn whole-projection norms + rotation + page write", left, channels, rotate_store,
+                  (None, moved(tokens_n, channels)), moved(batch, channels))
+    bench.measure("virulix query temperature + page write", theirs, channels, plain_store,
+                  (None, moved(tokens_n, channels)), moved(batch, channels))
+    q_in = H * (latent.plain_dim + latent.rot_dim)
+    stacked = q_in + row + H
+    def latent_tail(ctx, x, view):
+        projected = x[:, :stacked].contiguous()
+        return bench.timed(lambda: latent.prepare(ctx, projected, view))
+    fold_flops = 2.0 * H * latent.plain_dim * latent.latent_dim
+    bench.measure("larolorn latent norm + rotation + page write, queries through the key expansion", latent,
+                  stacked, latent_tail, (fold_flops * tokens_n, None),
+                  batch * (q_in + H * row) * 2 + H * latent.plain_dim * latent.latent_dim * 2)
+    def latent_values(ctx, x, view):
+        attended = x[:, :H * latent.value_width].contiguous()
+        projected = x[:, :stacked].contiguous()
+        return bench.timed(lambda: latent.expand(ctx, attended, projected))
+    bench.measure("larolorn value expansion with the head gates", latent, max(stacked, H * latent.value_width), latent_values,
+                  (2.0 * H * latent.value_dim * latent.latent_dim * tokens_n, None),
+                  batch * H * (latent.value_width + latent.value_dim) * 2 + H * latent.value_dim * latent.latent_dim * 2)
+
+    # ---- the recurrences: float32 on the CUDA cores by both designs, so the prompt's bound is the float32 FMA rate
+    fma = (148 * 128 * 2 * 1.9e9, "of the float32 FMA rate (72 TFLOP/s nominal)")
+    ours = pair.right
+    oh, od, oe = ours.n_heads, ours.key_dim, ours.value_dim
+    ours_width = ours.projection.out_features
+    def decay_scan(ctx, x, view):
+        projected = x[:, :ours_width].contiguous()
+        view = view[-1] if isinstance(view, tuple) else view
+        return bench.timed(lambda: ours.scan(ctx, projected, view))
+    bench.measure("larolorn decayed linear attention scan", ours, ours_width, decay_scan, (5.0 * oh * od * oe * tokens_n, None),
+                  batch * oh * od * oe * 4 * 2, prompt_of=fma)
+    gh, gd, ge = their_gla.n_heads, their_gla.key_dim, their_gla.value_dim
+    their_width = their_gla.projection.out_features
+    def gla_scan(ctx, x, view):
+        projected = x[:, :their_width].contiguous()
+        mixed = torch.empty((x.shape[0], gh * ge), dtype=x.dtype, device=x.device)
+        bench.timed(lambda: their_gla.scan(ctx, projected, view, mixed))
+        return mixed
+    bench.measure("virulix gated linear attention scan (decay per channel)", their_gla, max(their_width, 8), gla_scan,
+                  (5.0 * gh * gd * ge * tokens_n, None), batch * gh * gd * ge * 4 * 2, prompt_of=fma)
+    def whole_norm_gate(ctx, x, view):
+        projected = x[:, :ours_width].contiguous()
+        raw = projected[:, :oh * oe].float()
+        mixed = torch.empty((x.shape[0], oh * oe), dtype=x.dtype, device=x.device)
+        bench.timed(lambda: ops.lin_norm_gate_whole(raw, projected, ours.columns[3], ours.norm_weight.data, ours.norm_eps, mixed))
+        return mixed
+    gate_bytes = lambda n: n * oh * oe * (4 + 2 + 2)
+    bench.measure("larolorn norm over all heads + gate", ours, ours_width, whole_norm_gate, (None, gate_bytes(tokens_n)),
+                  gate_bytes(batch))
+
+    # ---- joining the stream, and the feed-forwards
+    def join(ctx, x, view):
+        stream = x[:, :W].float()
+        a, b = x[:, :W].float() * 3.0, x[:, :W].float() * 0.1
+        weight = torch.ones(W, dtype=pair.left_weight.data.dtype, device=x.device)
+        return bench.timed(lambda: ops.rms_join(stream, a, weight, 1e-6, 0.5, b=b, weight_a=pair.left_weight.data,
+                                                weight_b=pair.right_weight.data, pre=0.5))
+    join_bytes = lambda n: n * W * 4 * 4               # the stream read and written, two float32 branches read
+    bench.measure("larolorn two normed branches join the stream (1 kernel)", latent, W, join, (None, join_bytes(tokens_n)),
+                  join_bytes(batch))
+    def feed_forward(part, **how):
+        def kernel(ctx, x, view):
+            h = x[:, :W].contiguous()
+            return bench.timed(lambda: part.forward(ctx, h, **how))
+        return kernel
+    dense = next(l.feed_forward for l in larolorn.layers if l.feed_forward is not None)
+    inner = dense.intermediate_size
+    bench.measure("larolorn feed-forward (clamped, float32 result)", dense, W, feed_forward(dense, out_float32=True),
+                  (2.0 * tokens_n * 3 * inner * W, None), 3 * inner * W * 2)
+    gated = next(l.feed_forward for l in virulix.layers if hasattr(l.feed_forward, "gate_up"))
+    bench.measure("virulix feed-forward (gated gelu)", gated, W, feed_forward(gated), (2.0 * tokens_n * 3 * inner * W, None),
+                  3 * inner * W * 2)
+    return bench.rows
+
+
+def run_larolorn(args):
+    """Prefill and decode of Larolorn at sizes like a real model's layers, beside Virulix (the engine's closest design:
+    a float32 stream, attention layers and linear-attention layers with a float32 state) of equal width, heads, layer
+    count, feed-forward size and vocabulary, and the kernels of its mechanisms against their rooflines."""
+    import torch
+    from qwen_inference_lab_b200.config.model_config import LarolornConfig, VirulixConfig
+    from qwen_inference_lab_b200.loading import random_model
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for name in ([args.larolorn_shape] if args.larolorn_shape else sorted(LAROLORN_SHAPES)):
+        sizes = LAROLORN_SHAPES[name]
+        larolorn = random_model(LarolornConfig.from_dict(_larolorn_sizes(**sizes)), seed=0, device="cuda", dtype=torch.bfloat16)
+        virulix = random_model(VirulixConfig.from_dict(_virulix_beside_larolorn(**sizes)), seed=0, device="cuda", dtype=torch.bfloat16)
+        result = {"workload": "larolorn", "width": sizes["width"], "layers": 8, "dtype": "bfloat16",
+                  "peaks": "of measured" if pk["source"] == "measured" else "of fallback", "models": {}, "kernels": []}
+        for label, model in (("larolorn", larolorn), ("virulix", virulix)):
+            bench = _ModelBench(model, sizes["vocab"])
+            entry = {}
+            for tokens_n in (512, 2048):
+                ms = bench.prefill(tokens_n, flush)
+                entry[f"prefill_{tokens_n}"] = {"ms": round(ms, 3), "tokens_per_s": round(tokens_n / ms * 1e3, 1)}
+            for batch, context in ((1, 2048), (8, 2048), (32, 2048)):
+                ms = bench.decode(batch, context, args.steps, max(args.warmup, 6))
+                entry[f"decode_b{batch}_c{context}"] = {"ms": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3, 1)}
+            result["models"][label] = entry
+        for kernel, ms, frac, of in _larolorn_kernels(torch, larolorn, virulix, sizes, pk, 2048, 8, 2048 + 511, flush):
+            result["kernels"].append({"kernel": kernel, "ms": round(ms, 4), "frac": round(frac, 4), "of": of})
+        print(json.dumps(result), flush=True)
+        del larolorn, virulix
+        torch.cuda.empty_cache()
+
+
 def run_reference(args):
     ref = ROOT / "baseline" / "_ref"
     def unavailable(why):
@@ -915,15 +1175,18 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     parser.add_argument("--quick", action="store_true", help="skip the batch 1 and 64 points")
-    parser.add_argument("--only", choices=["decode", "prefill", "mixed", "virulix", "debisun"], default=None,
+    parser.add_argument("--only", choices=["decode", "prefill", "mixed", "virulix", "debisun", "larolorn"], default=None,
                         help="run just this part and print its result instead of the JSON line; mixed = 64 requests "
                              "with prompts of 16 to 2048 tokens and 128 new tokens each through Engine.generate; "
                              "virulix = the Virulix design beside dense Qwen3 of equal size, and its mixers' kernels; "
-                             "debisun = the Debisun design beside Virulix of equal size, and its mechanisms' kernels")
+                             "debisun = the Debisun design beside Virulix of equal size, and its mechanisms' kernels; "
+                             "larolorn = the Larolorn design beside Virulix of equal size, and its mechanisms' kernels")
     parser.add_argument("--virulix-shape", choices=sorted(VIRULIX_SHAPES), default=None,
                         help="width of --only virulix (default: all)")
     parser.add_argument("--debisun-shape", choices=sorted(DEBISUN_SHAPES), default=None,
                         help="width of --only debisun (default: all)")
+    parser.add_argument("--larolorn-shape", choices=sorted(LAROLORN_SHAPES), default=None,
+                        help="width of --only larolorn (default: all)")
     parser.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes (default: Qwen3-8B)")
     parser.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     parser.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per request (profiling aid)")
@@ -937,6 +1200,9 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.only == "larolorn":
+        run_larolorn(args)
+        return
     if args.only == "debisun":
         run_debisun(args)
         return 0

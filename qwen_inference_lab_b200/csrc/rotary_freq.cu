@@ -261,3 +261,30 @@ extern "C" int qil_head_product(const void* x, long long x_row, int x_head, cons
     if (err != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(err)); return (int)err; }
     QIL_CHECK_LAUNCH();
 }
+
+// y[n, h * width + j] *= sigmoid(gate[n, h]): a gate per token and head on rows laid out head by head (float32 math,
+// one rounding).  For steps whose per-head products ran as one batched library product.
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_gate_kernel(T* __restrict__ y, long long y_row, int width, const T* __restrict__ gate, long long gate_row, int n_heads) {
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const size_t token = blockIdx.x;
+    const int per_row = n_heads * width;
+    for (int i = threadIdx.x; i < per_row; i += 256) {
+        const float g = to_f32<T>(gate[token * gate_row + i / width]);
+        T* at = y + token * y_row + i;
+        *at = from_f32<T>(to_f32<T>(*at) / (1.f + expf(-g)));
+    }
+}
+
+extern "C" int qil_head_gate(void* y, long long y_row, int width, const void* gate, long long gate_row, int n_tokens,
+                             int n_heads, int act_dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_heads <= 0 || width <= 0) QIL_REFUSE("head_gate: %d heads of %d", n_heads, width);
+    QIL_DISPATCH_1(act_dtype, {
+        qil_launch_chained(head_gate_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (T*)y, y_row, width, (const T*)gate,
+                           gate_row, n_heads);
+    });
+    QIL_CHECK_LAUNCH();
+}

@@ -878,6 +878,20 @@ def head_product(x, x_column, x_head_stride, weight, y, y_column, y_head_stride,
     return y
 
 
+def head_gate(y, width, gate, gate_column):
+    """y[n, h * width + j] *= sigmoid(gate[n, gate_column + h]) in place: a gate per token and head on rows laid out
+    head by head (float32 arithmetic, one rounding)."""
+    _need(y, "y", ndim=2); _need(gate, "gate", y.dtype, 2)
+    n = y.shape[0]
+    if width <= 0 or y.shape[1] % width or gate.shape[0] != n or gate_column + y.shape[1] // width > gate.shape[1]:
+        raise KernelError("head_gate: the gate's columns do not match the heads")
+    lib = core()
+    _check(lib, lib.qil_head_gate(_p(y), c_longlong(y.shape[1]), c_int(width),
+                                  c_void_p(gate.data_ptr() + gate_column * gate.element_size()), c_longlong(gate.shape[1]),
+                                  c_int(n), c_int(y.shape[1] // width), c_int(dtype_code(y.dtype)), _stream()), "head_gate")
+    return y
+
+
 def moe_route(x, router, bias, top, *, softmax_all=False, correction=None, weight_scale=1.0, gate_row=False):
     """(chosen int32 [N, top], weights float32 [N, top]): the ``top`` largest of x R^T + b per row (float32
     arithmetic; the lower index wins a tie) and the softmax over those logits alone.

@@ -14,7 +14,9 @@ Only z and rot(s) are cached: the products with Wuk and Wuv are moved to the que
 the same key row [z, rot(s)] (attention with one key/value head), the weighted sum runs over the z_j, and Wuv_a is
 applied once to that sum.  Kernels: the stacked projection (q, dkv, g); ``ops.latent_prepare`` (norm of the latent,
 the rotations, the page write); ``ops.head_product`` (the query through Wuk^T); the engine's paged attention with a
-window; ``ops.head_product`` again (the sum through Wuv, times the gate); the output product.
+window; ``ops.head_product`` again (the sum through Wuv, times the gate); the output product.  A bfloat16 step of more
+than ``LIBRARY_ROWS`` tokens hands the two per-head products to the library as batched products over strided views
+of the same buffers (as ``Linear`` does with its products), and ``ops.head_gate`` applies the gates.
 
 A page holds the token's key row [z, rot(s)] and its value row.  Where c + r is a head size the tensor-core
 attention takes (a multiple of 16 up to 256), the value row is z followed by r zeros, so that keys and values
@@ -29,6 +31,9 @@ from .attention import _PLANNER
 from .base import KVCacheSpec, Mixer, Param
 from .linear import Linear, StackedLinear
 from .rotary import RotaryFrequencies
+
+
+LIBRARY_ROWS = 64      # bfloat16 steps of more tokens than this run the per-head products as batched library products
 
 
 class LatentAttention(Mixer):
@@ -83,22 +88,55 @@ class LatentAttention(Mixer):
 
     def forward(self, ctx, x, cache, residual=None, out_float32=False):
         """x [N, hidden] -> [N, hidden] (+ residual); ``cache`` is a KVCacheView of rows [latent, rotated key part]."""
-        n, heads, width = x.shape[0], self.n_heads, self.key_width
         projected = self.projection.forward(ctx, x)
+        queries = self.prepare(ctx, projected, cache)
+        attended = self.attend(ctx, queries, cache)
+        mixed = self.expand(ctx, attended, projected)
+        return self.out.forward(ctx, mixed, residual=residual, out_float32=out_float32)
+
+    def _batched(self, projected):
+        return projected.shape[0] > LIBRARY_ROWS and projected.dtype == torch.bfloat16 \
+            and self._query_fold.dtype == torch.bfloat16
+
+    def prepare(self, ctx, projected, cache):
+        """The projection's tail: the token's key row into its page, the queries [N, H * (c + r)] as the attention
+        reads them (plain part through Wuk^T, rotated part turned)."""
+        n, heads, width = projected.shape[0], self.n_heads, self.key_width
         queries = ctx.empty((n, heads * width))
         rotation = self.position
         ops.latent_prepare(projected, self.columns[0], self.columns[1], queries, cache.pages, self.latent_norm.data,
                            self.norm_eps, rotation.freq, rotation.rotary_dim, rotation.layout, ctx.positions, ctx.token_row,
                            cache.block_table, heads, self.plain_dim, self.rot_dim, self.latent_dim, self.value_width,
                            cache.page_size)
-        ops.head_product(projected, self.columns[0], self.plain_dim + self.rot_dim, self._query_fold, queries, 0, width)
+        if self._batched(projected):
+            plain = projected[:, :self.columns[1]].unflatten(1, (heads, self.plain_dim + self.rot_dim))[:, :, :self.plain_dim]
+            torch.bmm(plain.transpose(0, 1), self._query_fold.transpose(1, 2),
+                      out=queries.view(n, heads, width)[:, :, :self.latent_dim].transpose(0, 1))
+        else:
+            ops.head_product(projected, self.columns[0], self.plain_dim + self.rot_dim, self._query_fold, queries, 0, width)
+        return queries
+
+    def attend(self, ctx, queries, cache):
+        """Every head over the one key row per token: [N, H * value_width] weighted sums of latents."""
+        n, heads, width = queries.shape[0], self.n_heads, self.key_width
         attended = ctx.empty((n, heads * self.value_width))
         if queries.dtype == torch.bfloat16 and self.value_width == width:
             attention_mma.attend(ctx, queries, cache, attended, heads, 1, width, self.window, self.scale)
         else:
             ops.attention_generic(queries, cache.pages, attended, ctx.positions, ctx.token_row, cache.block_table, heads, 1,
                                   width, cache.page_size, self.window, self.scale, v_dim=self.value_width)
+        return attended
+
+    def expand(self, ctx, attended, projected):
+        """The weighted sums through Wuv, times the heads' gates: [N, H * e]."""
+        n, heads = attended.shape[0], self.n_heads
         mixed = ctx.empty((n, heads * self.value_dim))
-        ops.head_product(attended, 0, self.value_width, self._value_unfold, mixed, 0, self.value_dim,
-                         gate=projected, gate_column=self.columns[2])
-        return self.out.forward(ctx, mixed, residual=residual, out_float32=out_float32)
+        if self._batched(projected):
+            sums = attended.view(n, heads, self.value_width)[:, :, :self.latent_dim]
+            torch.bmm(sums.transpose(0, 1), self._value_unfold.transpose(1, 2),
+                      out=mixed.view(n, heads, self.value_dim).transpose(0, 1))
+            ops.head_gate(mixed, self.value_dim, projected, self.columns[2])
+        else:
+            ops.head_product(attended, 0, self.value_width, self._value_unfold, mixed, 0, self.value_dim,
+                             gate=projected, gate_column=self.columns[2])
+        return mixed

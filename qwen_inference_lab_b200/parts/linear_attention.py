@@ -186,8 +186,15 @@ class DecayLinearAttention(Mixer):
 
     def forward(self, ctx, x, cache, residual=None, out_float32=False):
         """x [N, hidden] -> [N, hidden] (+ residual); ``cache`` is a StateView with one slot per request row."""
-        n, heads, d, e = x.shape[0], self.n_heads, self.key_dim, self.value_dim
         projected = self.projection.forward(ctx, x)
+        raw = self.scan(ctx, projected, cache)
+        mixed = ctx.empty((x.shape[0], self.n_heads * self.value_dim))
+        ops.lin_norm_gate_whole(raw, projected, self.columns[3], self.norm_weight.data, self.norm_eps, mixed)
+        return self.out.forward(ctx, mixed, residual=residual, out_float32=out_float32)
+
+    def scan(self, ctx, projected, cache):
+        """The recurrence over the step's segments: ``projected`` -> the un-normed outputs, float32 [N, heads * e]."""
+        n, heads, d, e = projected.shape[0], self.n_heads, self.key_dim, self.value_dim
         plan = ctx.plans[_PLANNER.key]
         raw = ctx.empty((n, heads * e), dtype=torch.float32)
         common = (projected, self.columns, None, 1.0, None, self.norm_eps)
@@ -203,6 +210,4 @@ class DecayLinearAttention(Mixer):
             ops.gla_scan(*common, states, *chunk, heads, d, e, None, mode=ops.GLA_OWN_STATE, decay_product=decays, **options)
             ops.gla_carry(states, decays, cache.slots, plan.array["carry"], plan.count["carry"] // 3)
             ops.gla_scan(*common, states, *chunk, heads, d, e, None, scratch=raw, mode=ops.GLA_FROM_STATE, **options)
-        mixed = ctx.empty((n, heads * e))
-        ops.lin_norm_gate_whole(raw, projected, self.columns[3], self.norm_weight.data, self.norm_eps, mixed)
-        return self.out.forward(ctx, mixed, residual=residual, out_float32=out_float32)
+        return raw
