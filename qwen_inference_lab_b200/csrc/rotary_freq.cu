@@ -21,16 +21,22 @@
 // [N][H][c + r] (the first c columns receive the query folded through the key expansion, by another kernel).
 #include "common.cuh"
 
-__device__ __forceinline__ float rotated_element(const float* __restrict__ vec, int j, int rot_dims, int layout, int pos,
-                                                 const float* __restrict__ freq) {
+// The token's angles, once a block: table[i] = cos(pos * freq[i]), table[half + i] = sin(pos * freq[i]), i < half.
+// The caller puts a barrier between this and the first rotated_element.
+__device__ __forceinline__ void angle_table(float* __restrict__ table, int rot_dims, int pos, const float* __restrict__ freq) {
+    const int half = rot_dims >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * freq[i], &table[half + i], &table[i]);
+}
+
+__device__ __forceinline__ float rotated_element(const float* __restrict__ vec, int j, int rot_dims, int layout,
+                                                 const float* __restrict__ table) {
     // vec: the vector's values in float32 (shared memory); returns element j after rotation
     if (j >= rot_dims) return vec[j];
     const int half = rot_dims >> 1;
     int i, first, second;
     if (layout == 0) { i = j < half ? j : j - half; first = i; second = i + half; }
     else { i = j >> 1; first = 2 * i; second = 2 * i + 1; }
-    float s, c;
-    sincosf((float)pos * freq[i], &s, &c);
+    const float c = table[i], s = table[half + i];
     const float u = vec[first], v = vec[second];
     return j == first ? u * c - v * s : v * c + u * s;
 }
@@ -42,7 +48,7 @@ qk_rotate_store_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col,
                        const float* __restrict__ freq, int rot_dims, int layout, const int* __restrict__ positions,
                        const int* __restrict__ token_row, const int* __restrict__ block_table, int table_stride,
                        int n_q_heads, int n_kv_heads, int d, int e, int page_size, int num_pages) {
-    extern __shared__ float vals[];          // [Hq * d + Hkv * d]: q then k, normed, float32
+    extern __shared__ float vals[];          // [Hq * d + Hkv * d]: q then k, normed, float32;  then [rot_dims]: the angles
     __shared__ float scratch[32];
     qil_wait_for_producer();
     qil_release_consumer();
@@ -50,6 +56,8 @@ qk_rotate_store_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col,
     const int pos = positions[token];
     const int q_width = n_q_heads * d, k_width = n_kv_heads * d, v_width = n_kv_heads * e;
     const T* row = proj + (size_t)token * ld;
+    const float* table = vals + q_width + k_width;
+    angle_table(vals + q_width + k_width, rot_dims, pos, freq);
     float sq = 0.f, sk = 0.f;
     for (int i = tid; i < q_width; i += 256) { const float x = to_f32<T>(row[q_col + i]); vals[i] = x; sq = fmaf(x, x, sq); }
     for (int i = tid; i < k_width; i += 256) { const float x = to_f32<T>(row[k_col + i]); vals[q_width + i] = x; sk = fmaf(x, x, sk); }
@@ -65,7 +73,7 @@ qk_rotate_store_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col,
     T* q_dst = q_out + (size_t)token * q_width;
     for (int i = tid; i < q_width; i += 256) {
         const int head = i / d, j = i - head * d;
-        q_dst[i] = from_f32<T>(rotated_element(vals + head * d, j, rot_dims, layout, pos, freq));
+        q_dst[i] = from_f32<T>(rotated_element(vals + head * d, j, rot_dims, layout, table));
     }
     if (n_kv_heads == 0) return;
     const int index = pos / page_size;
@@ -76,7 +84,7 @@ qk_rotate_store_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col,
     for (int i = tid; i < k_width; i += 256) {
         const int head = i / d, j = i - head * d;
         page_base[((size_t)head * page_size + slot) * d + j] =
-            from_f32<T>(rotated_element(vals + q_width + head * d, j, rot_dims, layout, pos, freq));
+            from_f32<T>(rotated_element(vals + q_width + head * d, j, rot_dims, layout, table));
     }
     T* v_base = page_base + (size_t)n_kv_heads * page_size * d;
     for (int i = tid; i < v_width; i += 256) {
@@ -97,7 +105,7 @@ extern "C" int qil_qk_rotate_store(const void* proj, int ld, int q_col, int k_co
         QIL_REFUSE("qk_rotate_store: %d rotated dimensions of %d, layout %d", rot_dims, d, layout);
     if ((q_norm_w == nullptr) != (k_norm_w == nullptr) && n_kv_heads > 0)
         QIL_REFUSE("qk_rotate_store: give both norm weights or neither");
-    const size_t smem = (size_t)(n_q_heads + n_kv_heads) * d * sizeof(float);
+    const size_t smem = ((size_t)(n_q_heads + n_kv_heads) * d + rot_dims) * sizeof(float);
     if (smem > 160 * 1024) QIL_REFUSE("qk_rotate_store: %d values of q and k per token are too many", (n_q_heads + n_kv_heads) * d);
     cudaError_t err = cudaSuccess;
     QIL_DISPATCH_2(act_dtype, norm_dtype, {
@@ -120,7 +128,7 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_col, int kv_col,
                       const int* __restrict__ positions, const int* __restrict__ token_row,
                       const int* __restrict__ block_table, int table_stride, int n_heads, int d, int r, int c,
                       int value_width, int page_size, int num_pages) {
-    extern __shared__ float vals[];          // [c + r]: the latent row;  then [H * r]: the queries' rotated parts
+    extern __shared__ float vals[];          // [c + r]: the latent row;  [H * r]: the queries' rotated parts;  [rot_dims]: the angles
     __shared__ float scratch[32];
     qil_wait_for_producer();
     qil_release_consumer();
@@ -128,6 +136,8 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_col, int kv_col,
     const int pos = positions[token];
     const T* row = proj + (size_t)token * ld;
     float* q_rot = vals + c + r;
+    const float* table = q_rot + n_heads * r;
+    angle_table(q_rot + n_heads * r, rot_dims, pos, freq);
     float ss = 0.f;
     for (int i = tid; i < c + r; i += 256) {
         const float x = to_f32<T>(row[kv_col + i]);
@@ -144,7 +154,7 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_col, int kv_col,
     T* q_dst = q_att + (size_t)token * n_heads * width;
     for (int i = tid; i < n_heads * r; i += 256) {
         const int head = i / r, j = i - head * r;
-        q_dst[head * width + c + j] = from_f32<T>(rotated_element(q_rot + head * r, j, rot_dims, layout, pos, freq));
+        q_dst[head * width + c + j] = from_f32<T>(rotated_element(q_rot + head * r, j, rot_dims, layout, table));
     }
     const int index = pos / page_size;
     const int page = (pos >= 0 && index < table_stride) ? block_table[(size_t)token_row[token] * table_stride + index] : -1;
@@ -158,7 +168,7 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_col, int kv_col,
             key[i] = z;
             value[i] = z;
         } else {
-            key[i] = from_f32<T>(rotated_element(vals + c, i - c, rot_dims, layout, pos, freq));
+            key[i] = from_f32<T>(rotated_element(vals + c, i - c, rot_dims, layout, table));
         }
     }
     for (int i = c + tid; i < value_width; i += 256) value[i] = from_f32<T>(0.f);
@@ -174,7 +184,7 @@ extern "C" int qil_latent_prepare(const void* proj, int ld, int q_col, int kv_co
         QIL_REFUSE("latent_prepare: heads %d sizes %d/%d latent %d values %d page %d", n_heads, d, r, c, value_width, page_size);
     if (rot_dims < 0 || rot_dims > r || (rot_dims & 1) || (rot_dims > 0 && freq == nullptr) || (layout != 0 && layout != 1))
         QIL_REFUSE("latent_prepare: %d rotated dimensions of %d, layout %d", rot_dims, r, layout);
-    const size_t smem = (size_t)(c + r + n_heads * r) * sizeof(float);
+    const size_t smem = (size_t)(c + r + n_heads * r + rot_dims) * sizeof(float);
     if (smem > 160 * 1024) QIL_REFUSE("latent_prepare: %d values per token are too many", c + r + n_heads * r);
     cudaError_t err = cudaSuccess;
     QIL_DISPATCH_2(act_dtype, norm_dtype, {

@@ -184,7 +184,9 @@ LATENTS = [cases.latent(3, 24, 8, 40, 24, 0.17, 10000.0, 20),      # key rows of
            cases.latent(5, 12, 4, 20, 10, 0.25, 2000.0, 1),        # rows of 14: the float32 kernel; a token sees itself
            cases.latent(1, 6, 2, 10, 30, 0.4, 7.0, 4096),          # one head, one rotated pair, no window in reach
            cases.latent(2, 16, 16, 16, 48, 0.18, 100.0, 33),       # rows of 64
-           cases.latent(4, 40, 24, 8, 72, 0.1, 1e6, 5)]            # rows of 96, values smaller than keys, a window of five
+           cases.latent(4, 40, 24, 8, 72, 0.1, 1e6, 5),            # rows of 96, values smaller than keys, a window of five
+           cases.latent(3, 48, 32, 56, 128, 0.09, 50000.0, 40),    # rows of 160
+           cases.latent(2, 128, 64, 128, 192, 0.07, 10000.0, 70)]  # rows of 256, the widest the tensor-core kernels take
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
@@ -206,7 +208,9 @@ LEFTS = [cases.left(4, 2, 32, 32, 0.2, 300000.0, 16, 24),          # the tensor-
          cases.left(6, 3, 16, 8, 0.3, 1000.0, 16, 7),              # values smaller than keys: the float32 kernel
          cases.left(3, 3, 20, 12, 0.22, 50.0, 4, 1),               # a chunk of one position: a token and the sink
          cases.left(2, 1, 80, 80, 0.11, 500.0, 80, 4096),          # one key/value head, no chunk edge in reach
-         cases.left(6, 1, 16, 16, 0.25, 10000.0, 2, 33)]           # six query heads on one key/value head, one rotated pair
+         cases.left(6, 1, 16, 16, 0.25, 10000.0, 2, 33),           # six query heads on one key/value head, one rotated pair
+         cases.left(8, 2, 128, 128, 0.08, 500000.0, 64, 50),       # heads of 128, half of each rotated
+         cases.left(4, 4, 48, 48, 0.15, 20000.0, 48, 19)]          # heads of 48, as many key/value heads as query heads
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
