@@ -875,6 +875,9 @@ class _PartKernels:
     def timed(self, fn):
         torch = self.torch
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # the device idles for a moment while the host queues what follows, so that the two events bracket the
+        # kernels' time on the device and not the time the host takes to launch them
+        torch.cuda._sleep(400_000)
         start.record()
         out = fn()
         stop.record()

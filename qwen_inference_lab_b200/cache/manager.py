@@ -20,7 +20,8 @@ limit reserves nothing and grows until the free list is empty (trace replay).
 
 Layout of a group's storage: ``[member, page, 2 (K,V), kv_head, slot, head_dim]``; where values have
 another size than keys, ``[member, page, kv_head * slot * (head_dim + v_head_dim)]``: a page's key rows
-``[kv_head, slot, head_dim]`` followed by its value rows ``[kv_head, slot, v_head_dim]``.
+``[kv_head, slot, head_dim]`` followed by its value rows ``[kv_head, slot, v_head_dim]``; where a position's value is
+the head of its key (``shared_rows``), ``[member, page, 1, kv_head, slot, head_dim]``.
 """
 from __future__ import annotations
 
@@ -60,7 +61,9 @@ class _KVGroup:
     def __init__(self, spec, members, num_pages, page_size, max_requests, table_width, dtype, device):
         self.spec, self.members = spec, list(members)
         self.capacity, self.page_size = int(num_pages), int(page_size)
-        if spec.value_dim == spec.head_dim:
+        if spec.shared_rows:   # one row per position: the key, whose leading columns are the value
+            shape = (len(self.members), num_pages, 1, spec.kv_heads, page_size, spec.head_dim)
+        elif spec.value_dim == spec.head_dim:
             shape = (len(self.members), num_pages, 2, spec.kv_heads, page_size, spec.head_dim)
         else:     # a page's key rows, then its value rows
             shape = (len(self.members), num_pages, spec.kv_heads * page_size * (spec.head_dim + spec.value_dim))

@@ -19,7 +19,8 @@
 // which for equal sizes is the layout [2][kv_head][slot][head_dim].  And a bias
 // that grows with distance may be taken off the scaled score (`slopes`, one per
 // query head): score = q.k * scale - slope_h * (i - j) for the query at position i
-// and the key at position j.
+// and the key at position j.  With `shared_rows` a page holds its key rows only, and
+// a position's value is the first `v_dim` columns of its key.
 //
 // Further options of the score, all in float32 (`ScoreOptions`):
 //   softcap     score <- cap * tanh(score / cap), applied to the scaled product before any bias
@@ -51,7 +52,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache
                          const int* __restrict__ positions, const int* __restrict__ token_row,
                          const int* __restrict__ block_table, int table_stride,
                          int n_q_heads, int n_kv_heads, int head_dim, int v_dim, int page_size, int num_pages,
-                         int window, float scale, const float* __restrict__ slopes, ScoreOptions opt) {
+                         int window, float scale, const float* __restrict__ slopes, ScoreOptions opt, int shared_rows) {
     extern __shared__ long long smem_ll[];
     long long* row_off = smem_ll;                      // [GEN_TILE] element offset of each key row, -1 if none
     long long* val_off = row_off + GEN_TILE;           // [GEN_TILE] element offset of each value row
@@ -79,7 +80,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache
 #pragma unroll
     for (int i = 0; i < GEN_DPT; ++i) acc[i] = 0.f;
 
-    const long long page_elems = (long long)n_kv_heads * page_size * (head_dim + v_dim);
+    const long long page_elems = (long long)n_kv_heads * page_size * (shared_rows ? head_dim : head_dim + v_dim);
     const long long k_plane = (long long)n_kv_heads * page_size * head_dim;   // a page's key rows come first
     for (int tile = lo / GEN_TILE; tile * GEN_TILE <= pos; ++tile) {
         const int key = tile * GEN_TILE + tid;
@@ -90,7 +91,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache
             if (page >= 0 && page < num_pages) {
                 const long long row = (long long)kv_head * page_size + (key % page_size);
                 off = page * page_elems + row * head_dim;
-                voff = page * page_elems + k_plane + row * v_dim;
+                voff = shared_rows ? off : page * page_elems + k_plane + row * v_dim;
             }
         }
         __syncthreads();  // previous tile's readers of row_off / ps are done
@@ -150,11 +151,12 @@ extern "C" int qil_attention_generic(
     const void* q, const void* kv_cache, void* out, const int* positions, const int* token_row,
     const int* block_table, int table_stride, int n_tokens, int n_q_heads, int n_kv_heads,
     int head_dim, int v_dim, int page_size, int num_pages, int window, float scale, const float* slopes,
-    float softcap, const float* dist_bias, int dist_len, int chunk, int sink, const float* sink_logits, int act_dtype,
-    cudaStream_t stream) {
+    float softcap, const float* dist_bias, int dist_len, int chunk, int sink, const float* sink_logits, int shared_rows,
+    int act_dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (head_dim <= 0 || head_dim > GEN_MAX_D || v_dim <= 0 || v_dim > GEN_MAX_D)
         QIL_REFUSE("attention_generic: head sizes %d and %d must lie in 1..%d", head_dim, v_dim, GEN_MAX_D);
+    if (shared_rows && v_dim > head_dim) QIL_REFUSE("attention_generic: values of %d out of shared rows of %d", v_dim, head_dim);
     if (n_kv_heads <= 0 || n_q_heads <= 0 || n_q_heads % n_kv_heads)
         QIL_REFUSE("attention_generic: %d query heads do not divide into %d kv heads", n_q_heads, n_kv_heads);
     if (n_q_heads > 65535) QIL_REFUSE("attention_generic: too many heads (%d)", n_q_heads);
@@ -168,6 +170,6 @@ extern "C" int qil_attention_generic(
     QIL_DISPATCH_1(act_dtype,
         (attention_generic_kernel<T><<<grid, GEN_TILE, smem, stream>>>(
             (const T*)q, (const T*)kv_cache, (T*)out, positions, token_row, block_table, table_stride,
-            n_q_heads, n_kv_heads, head_dim, v_dim, page_size, num_pages, window, scale, slopes, opt)));
+            n_q_heads, n_kv_heads, head_dim, v_dim, page_size, num_pages, window, scale, slopes, opt, shared_rows)));
     QIL_CHECK_LAUNCH();
 }

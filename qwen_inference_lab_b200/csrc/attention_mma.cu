@@ -93,6 +93,10 @@ struct AttnParams {
     const int* block_table;
     int table_stride;
     int n_q_heads, n_kv_heads, page_size, num_pages, window;
+    // 2: a page holds its key rows [kv_head][slot][D] and then its value rows; 1 ("shared rows"): a page holds one
+    // row per (kv head, slot), which is the key, and whose leading columns are the value: no value row is stored
+    // or read, the value tile is the key tile, and the output's trailing columns hold sums the caller ignores
+    int planes;
     float scale_log2;         // head_dim^-1/2 * log2(e)
     // null, or one slope per query head, times log2(e): score = q.k * scale - slope_h * (query position - key position)
     const float* slopes_log2;
@@ -142,7 +146,7 @@ __device__ __forceinline__ int kv_row_offset(const AttnParams& p, const int* pag
     if (pos < lo || pos > hi || pos / p.page_size >= p.table_stride) return -1;
     const int page = pages[pos / p.page_size - first_page];
     if (page < 0 || page >= p.num_pages) return -1;
-    return (int)((((size_t)page * 2 * p.n_kv_heads + kv_head) * p.page_size + (pos % p.page_size)) * (D / 8));
+    return (int)((((size_t)page * p.planes * p.n_kv_heads + kv_head) * p.page_size + (pos % p.page_size)) * (D / 8));
 }
 
 // Queue the copies of 64 key rows and 64 value rows into shared memory; rows without an offset are
@@ -160,7 +164,7 @@ __device__ __forceinline__ void issue_kv_tile(const AttnParams& p, const int* ro
         const bool valid = off >= 0;
         const bf16* src = p.kv + (size_t)(valid ? off : 0) * 8 + piece * 8;
         cp_async16(sK + row * LDS + piece * 8, src, valid);
-        cp_async16(sV + row * LDS + piece * 8, src + v_plane, valid);
+        if (p.planes == 2) cp_async16(sV + row * LDS + piece * 8, src + v_plane, valid);
     }
 }
 
@@ -172,7 +176,7 @@ __device__ __forceinline__ void attn_prefill_tile(const AttnParams& p, const int
     // [K stage 0][K stage 1][V stage 0][V stage 1]; when the queries live in registers (head sizes up to
     // 128) their tile borrows K stage 1 until the fragments are loaded, else it has a region of its own
     bf16* sK = reinterpret_cast<bf16*>(smem_raw);      // [2][64][LDS]
-    bf16* sV = sK + 2 * KV_TILE * LDS;                  // [2][64][LDS]
+    bf16* sV = p.planes == 2 ? sK + 2 * KV_TILE * LDS : sK;   // [2][64][LDS]; shared rows: the key tiles themselves
     bf16* sQ = Q_IN_REGS ? sK + KV_TILE * LDS : sV + 2 * KV_TILE * LDS;   // [64][LDS]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kv_head = head / (p.n_q_heads / p.n_kv_heads);
@@ -545,7 +549,8 @@ __device__ __forceinline__ void attn_decode_span_block(
         Wait wait_for_inputs) {
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);      // [16][LDS]
     bf16* sK = sQ + 16 * LDS;                           // [2][64][LDS]
-    bf16* sV = sK + 2 * KV_TILE * LDS;                  // [2][64][LDS]
+    const bool shared = p.planes == 1;                  // the value rows are the key rows: see AttnParams
+    bf16* sV = shared ? sK : sK + 2 * KV_TILE * LDS;    // [2][64][LDS]
     int* s_pages = reinterpret_cast<int*>(sV + 2 * KV_TILE * LDS);   // [span_len / page_size + 2]
     // Up to qil_wait_for_producer() below only memory that no kernel of this step writes is read:
     // the step's description, the block table, and keys and values of earlier positions.
@@ -615,7 +620,7 @@ __device__ __forceinline__ void attn_decode_span_block(
     const bool early = first_tile != hi / KV_TILE;
     if (early) issue_rows(off0, my_k, 0);
     cp_async_commit();
-    if (early) issue_rows(off0, my_v, v_plane);
+    if (early && !shared) issue_rows(off0, my_v, v_plane);
     cp_async_commit();
     wait_for_inputs();
     if (tail.qkv == nullptr) {   // finished queries: the heads of this kv head, 8 threads per row
@@ -655,10 +660,10 @@ __device__ __forceinline__ void attn_decode_span_block(
         }
         __syncthreads();
     }
-    if (!early) { issue_rows(off0, my_k, 0); issue_rows(off0, my_v, v_plane); }
+    if (!early) { issue_rows(off0, my_k, 0); if (!shared) issue_rows(off0, my_v, v_plane); }
     if (first_tile + 1 <= last_tile) issue_rows(off1, my_k + BUFFER, 0);
     cp_async_commit();
-    if (first_tile + 1 <= last_tile) issue_rows(off1, my_v + BUFFER, v_plane);
+    if (first_tile + 1 <= last_tile && !shared) issue_rows(off1, my_v + BUFFER, v_plane);
     cp_async_commit();
     cp_async_wait<1>();          // the queries and the first tiles' keys; only the second tile's values may be under way
     __syncthreads();             // the query rows are every warp's
@@ -672,7 +677,10 @@ __device__ __forceinline__ void attn_decode_span_block(
     for (int tile = first_tile; tile <= last_tile; ++tile) {
         const int buf = (tile - first_tile) & 1;
         const int off2 = row_offset(tile + 2);
-        cp_async_wait<3>();          // this tile's keys: at most V(t), K(t+1), V(t+1) may still be under way
+        // this tile's keys: at most V(t), K(t+1), V(t+1) may still be under way.  With shared rows the groups that
+        // would hold values are empty up to V(1), and from tile 2 on a tile's rows travel in its V group (they
+        // replace rows that the output product still reads): one group fewer may be under way
+        if (shared) cp_async_wait<2>(); else cp_async_wait<3>();
         __syncwarp();
         if (Q_IN_REGS && tile == first_tile) {
 #pragma unroll
@@ -700,7 +708,7 @@ __device__ __forceinline__ void attn_decode_span_block(
             mma_bf16(s[1], a, b2, b3);
         }
         __syncwarp();                // every lane has read the keys: their rows take tile t + 2
-        if (tile + 2 <= last_tile) issue_rows(off2, my_k + buf * BUFFER, 0);
+        if (tile + 2 <= last_tile && !shared) issue_rows(off2, my_k + buf * BUFFER, 0);
         cp_async_commit();
         // every row is the same position: one mask for all (a row is a query head: each has its slope)
 #pragma unroll
@@ -750,7 +758,7 @@ __device__ __forceinline__ void attn_decode_span_block(
             mma_bf16(o[2 * dp + 1], a, b2, b3);
         }
         __syncwarp();
-        if (tile + 2 <= last_tile) issue_rows(off2, my_v + buf * BUFFER, v_plane);
+        if (tile + 2 <= last_tile) issue_rows(off2, my_v + buf * BUFFER, shared ? 0 : v_plane);
         cp_async_commit();
     }
     cp_async_wait<0>();
@@ -873,7 +881,7 @@ static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, 
     p.q = (const bf16*)q; p.kv = (const bf16*)kv; p.out = (bf16*)out;
     p.block_table = block_table; p.table_stride = table_stride;
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
-    p.window = window;
+    p.window = window; p.planes = 2;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.slopes_log2 = nullptr;
     p.scale = scale; p.softcap = 0.f; p.tanh_arg = p.cap_log2 = 0.f; p.dist_bias = nullptr; p.dist_len = 0; p.chunk = 0; p.sink = 0; p.sink_log2 = nullptr;
@@ -901,8 +909,8 @@ static bool has_options(const AttnParams& p) {
 
 // Shared memory of the span kernel: query rows, two stages of key and value tiles (reused for the
 // merge of the four warps), and the span's page ids.
-static int decode_smem_bytes(int span_len, int page_size) {
-    const int tile_bytes = (16 + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
+static int decode_smem_bytes(int span_len, int page_size, int planes = 2) {
+    const int tile_bytes = (16 + 2 * planes * KV_TILE) * LDS * (int)sizeof(bf16);
     return tile_bytes + (span_len / page_size + 3) * (int)sizeof(int);
 }
 
@@ -942,21 +950,24 @@ static int launch_prefill(const void* q, const void* kv, void* out, const int* t
                           const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                           int page_size, int num_pages, int window, float scale,
                           const float* slopes_log2, float softcap, const float* dist_bias, int dist_len, int chunk,
-                          int sink, cudaStream_t stream, const float* sink_log2 = nullptr) {
+                          int sink, cudaStream_t stream, const float* sink_log2 = nullptr, int planes = 2) {
     if (n_tiles <= 0) return 0;
     AttnParams p;
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
+    if (planes != 1 && planes != 2) QIL_REFUSE("attention: a page holds 1 or 2 rows per position, not %d", planes);
+    p.planes = planes;
     p.slopes_log2 = slopes_log2;
     if (fill_options(p, softcap, dist_bias, dist_len, chunk, sink, sink_log2)) return -1;
     if (n_tiles > 65535) QIL_REFUSE("attention: %d query tiles in one launch; at most 65535", n_tiles);
     if ((uintptr_t)tile_info & 15) QIL_REFUSE("attention: tile_info must be 16-byte aligned");
-    const int smem = ((Q_IN_REGS ? 0 : Q_TILE) + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
+    const int full = ((Q_IN_REGS ? 0 : Q_TILE) + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
+    const int smem = ((Q_IN_REGS ? 0 : Q_TILE) + 2 * planes * KV_TILE) * LDS * (int)sizeof(bf16);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, full);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, full);
+        if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", full, cudaGetErrorString(e));
         configured = true;
     }
     if (has_options(p)) attn_prefill_kernel<true><<<dim3(n_q_heads, n_tiles), 128, smem, stream>>>(p, (const int4*)tile_info);
@@ -983,6 +994,15 @@ extern "C" int qil_attn_prefill_modified(const void* q, const void* kv, void* ou
                           num_pages, 0, scale, slopes_log2, softcap, dist_bias, dist_len, chunk, sink, stream, sink_log2);
 }
 
+// The same over pages of one row per position (shared rows, see AttnParams): out's columns past the value's width
+// hold weighted sums of the rows' other columns.
+extern "C" int qil_attn_prefill_shared(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                       const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                                       int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
+    return launch_prefill(q, kv, out, tile_info, n_tiles, block_table, table_stride, n_q_heads, n_kv_heads, page_size,
+                          num_pages, window, scale, nullptr, 0.f, nullptr, 0, 0, 0, stream, nullptr, 1);
+}
+
 extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
                                 const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                                 int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
@@ -1005,11 +1025,14 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
                          int page_size, int num_pages, int window, float scale, const DecodeTail& tail,
                          cudaStream_t stream, const float* slopes_log2 = nullptr, float softcap = 0.f,
                          const float* dist_bias = nullptr, int dist_len = 0, int chunk = 0, int sink = 0,
-                         const float* sink_log2 = nullptr) {
+                         const float* sink_log2 = nullptr, int planes = 2) {
     if (n_decode <= 0) return 0;
     AttnParams p;
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
+    if (planes != 1 && planes != 2) QIL_REFUSE("attention: a page holds 1 or 2 rows per position, not %d", planes);
+    if (planes == 1 && tail.qkv != nullptr) QIL_REFUSE("attention: the projection's tail writes value rows; shared rows have none");
+    p.planes = planes;
     p.slopes_log2 = slopes_log2;
     if (fill_options(p, softcap, dist_bias, dist_len, chunk, sink, sink_log2)) return -1;
     if (check_decode_span(span_len, n_spans)) return -1;
@@ -1017,7 +1040,7 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
     if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention: decode_info must be 16-byte aligned");
     const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
     if (n_decode > 65535 || n_spans > 65535) QIL_REFUSE("attention: grid too large");
-    const int smem = decode_smem_bytes(span_len > 0 ? span_len : -span_len, page_size);
+    const int smem = decode_smem_bytes(span_len > 0 ? span_len : -span_len, page_size, planes);
     if (has_options(p)) {
         if (ensure_decode_smem(attn_decode_span_kernel<true>, smem, 1)) return -1;
         qil_launch_chained(attn_decode_span_kernel<true>, dim3(n_kv_heads * chunks, n_decode, n_spans), dim3(128), smem, stream,
@@ -1043,6 +1066,17 @@ extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const i
     DecodeTail none = {};
     return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, tickets, n_spans, span_len, block_table,
                          table_stride, n_q_heads, n_kv_heads, page_size, num_pages, window, scale, none, stream);
+}
+
+// The same over pages of one row per position (shared rows, see AttnParams).
+extern "C" int qil_attn_decode_shared(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
+                                      float* part_o, float* part_ml, unsigned* tickets, int n_spans, int span_len,
+                                      const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                                      int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
+    DecodeTail none = {};
+    return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, tickets, n_spans, span_len, block_table,
+                         table_stride, n_q_heads, n_kv_heads, page_size, num_pages, window, scale, none, stream,
+                         nullptr, 0.f, nullptr, 0, 0, 0, nullptr, 1);
 }
 
 // The same with a distance bias per query head (slopes_log2: float32 [n_q_heads], see AttnParams).

@@ -171,6 +171,12 @@ struct AtParams {
     float scale_log2;
     // null, or one slope per query head times log2(e): score = q.k * scale - slope_h * (query position - key position)
     const float* slopes_log2;
+    // chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0): the
+    // tiles start at the chunk of the tile's first row, and rows of a later chunk mask what lies before theirs
+    int chunk;
+    // null, or one learned score per query head times log2(e): exp2 of it joins the softmax's denominator, a key
+    // without a value whose score is neither scaled nor biased
+    const float* sink_log2;
     int* error_word;
     long long* trace;           // only read when compiled with AT_TRACE
 };
@@ -200,7 +206,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int4 info = tile_info[blockIdx.y];
     const int n0 = info.x, pos0 = info.y;
     const int hi = pos0 + AT_M - 1;                          // last key any row of the tile may see
-    const int n_tiles = hi / AT_N + 1;
+    const int tile0 = p.chunk > 0 ? pos0 / p.chunk * p.chunk / AT_N : 0;   // the key tile that holds the first key any row sees
+    const int n_tiles = hi / AT_N + 1 - tile0;
     const int* table = p.block_table + (size_t)info.w * p.table_stride;
 
     if (threadIdx.x == 0) {
@@ -257,12 +264,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         int my_page = -1;
         for (int j = 0; j < n_tiles; ++j) {
             if (j % tiles_per_batch == 0) {
-                const int index = j * pages_per_tile + lane;
+                const int index = (tile0 + j) * pages_per_tile + lane;
                 my_page = (index <= last_page && index < p.table_stride) ? table[index] : -1;
             }
             const int stage = j % AT_STAGES;
             const unsigned parity = ((j / AT_STAGES) & 1) ^ 1;
-            const int first_key = j * AT_N;
+            const int first_key = (tile0 + j) * AT_N;
             int pages = pages_per_tile;
             if (first_key + AT_N - 1 > hi) pages = (hi - first_key) / p.page_size + 1;
             const int pg = lane % pages_per_tile, half = (lane / pages_per_tile) & 1;
@@ -346,6 +353,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;                 // query row of this thread = its TMEM lane
         const int pos = pos0 + row;
+        const int lo = p.chunk > 0 ? pos / p.chunk * p.chunk : 0;   // the first key this row sees
         const unsigned lane_base = (unsigned)(quarter * 32) << 16;
         // With a distance bias the scores are scaled and biased first and the steps below take them as they are.
         const bool biased = p.slopes_log2 != nullptr;
@@ -375,15 +383,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // the row's maximum of the raw scores; the scale (positive) is applied to the maximum and, fused
             // with the subtraction, inside the exponent.  Four running maxima and four running sums: one
             // chain of 64 dependent operations would cost this warp, alone on its scheduler, their latency.
-            const int key0 = j * AT_N;
+            const int key0 = (tile0 + j) * AT_N;
             if (biased) {
                 const float base = slope * (float)(key0 - pos);
 #pragma unroll
                 for (int i = 0; i < AT_N; ++i) s[i] = fmaf(s[i], p.scale_log2, fmaf(slope, (float)i, base));
             }
-            if (key0 + AT_N - 1 > pos0) {
+            if (key0 + AT_N - 1 > pos0 || key0 < lo) {
 #pragma unroll
-                for (int i = 0; i < AT_N; ++i) s[i] = (key0 + i <= pos) ? s[i] : -INFINITY;
+                for (int i = 0; i < AT_N; ++i) s[i] = (key0 + i <= pos && key0 + i >= lo) ? s[i] : -INFINITY;
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -470,6 +478,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         if (ok) {
             at_fence_after();
+            if (p.sink_log2 != nullptr) l += (m_used == -INFINITY) ? 1.f : exp2f(p.sink_log2[head] - m_used);
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* dst = p.out + ((size_t)(n0 + row) * p.n_q_heads + head) * AT_D;
 #pragma unroll 1
@@ -521,12 +530,14 @@ extern "C" int qil_attn_tc_keys_per_tile() { return AT_N; }
 // page_size must divide the keys per tile and be a multiple of 8.  error_word: a device int, zeroed by the
 // caller once.  trace: null, or 3 * 1024 int64 for the time stamps of block (0, 0) in a build with AT_TRACE.
 // slopes_log2: null, or float32 [n_q_heads] on the device: a distance bias per query head (see AtParams).
-extern "C" int qil_attn_tc_prefill_biased(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+// chunk, sink_log2 (null, or float32 [n_q_heads] on the device): see AtParams.
+extern "C" int qil_attn_tc_prefill_masked(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
                                           int n_tokens, const int* block_table, int table_stride, int n_q_heads,
                                           int n_kv_heads, int page_size, int num_pages, float scale,
-                                          const float* slopes_log2, int* error_word, long long* trace,
-                                          cudaStream_t stream) {
+                                          const float* slopes_log2, int chunk, const float* sink_log2, int* error_word,
+                                          long long* trace, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
+    if (chunk < 0) QIL_REFUSE("attn_tc: chunks of %d positions", chunk);
     if (n_kv_heads <= 0 || n_q_heads % n_kv_heads) QIL_REFUSE("attn_tc: %d query heads, %d kv heads", n_q_heads, n_kv_heads);
     if (page_size < 8 || page_size > AT_N || AT_N % page_size || page_size % 8)
         QIL_REFUSE("attn_tc: pages of %d positions; this kernel takes multiples of 8 that divide %d", page_size, AT_N);
@@ -562,6 +573,7 @@ extern "C" int qil_attn_tc_prefill_biased(const void* q, const void* kv, void* o
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.slopes_log2 = slopes_log2;
+    p.chunk = chunk; p.sink_log2 = sink_log2;
     p.error_word = error_word;
     p.trace = trace;
     const int smem = AT_QTILE + 2 * AT_STAGES * AT_TILE + (int)sizeof(AtShared);
@@ -573,6 +585,16 @@ extern "C" int qil_attn_tc_prefill_biased(const void* q, const void* kv, void* o
     }
     attn_tc_kernel<<<dim3(n_q_heads, n_tiles), AT_THREADS, smem, stream>>>(map_q, map_kv, p, (const int4*)tile_info);
     QIL_CHECK_LAUNCH();
+}
+
+extern "C" int qil_attn_tc_prefill_biased(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                          int n_tokens, const int* block_table, int table_stride, int n_q_heads,
+                                          int n_kv_heads, int page_size, int num_pages, float scale,
+                                          const float* slopes_log2, int* error_word, long long* trace,
+                                          cudaStream_t stream) {
+    return qil_attn_tc_prefill_masked(q, kv, out, tile_info, n_tiles, n_tokens, block_table, table_stride, n_q_heads,
+                                      n_kv_heads, page_size, num_pages, scale, slopes_log2, 0, nullptr, error_word, trace,
+                                      stream);
 }
 
 extern "C" int qil_attn_tc_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,

@@ -159,13 +159,16 @@ extern "C" int qil_rms_scale_add(void* x, int x_dtype, const void* y, int y_dtyp
 template <typename TX, typename TA, typename W>
 __global__ void __launch_bounds__(256)
 rms_join_kernel(TX* __restrict__ x, const TA* __restrict__ a, const W* __restrict__ wa, const TA* __restrict__ b,
-                const W* __restrict__ wb, const W* __restrict__ w, int width, float eps, float pre, float mult) {
+                const W* __restrict__ wb, const W* __restrict__ w, int width, float eps, float pre, float mult,
+                bf16* __restrict__ rows) {
+    // rows: null, or [N, width]: the stream's new values once more, rounded to bfloat16 (what the next product reads)
     extern __shared__ float y[];             // [width] when there are two branches
     __shared__ float scratch[32];
     qil_wait_for_producer();
     qil_release_consumer();
     const TA* ra = a + (size_t)blockIdx.x * width;
     TX* dst = x + (size_t)blockIdx.x * width;
+    bf16* copy = rows != nullptr ? rows + (size_t)blockIdx.x * width : nullptr;
     float sa = 0.f, sb = 0.f;
     for (int i = threadIdx.x; i < width; i += 256) {
         const float v = to_f32<TA>(ra[i]);
@@ -174,8 +177,11 @@ rms_join_kernel(TX* __restrict__ x, const TA* __restrict__ a, const W* __restric
     sa = block_sum(sa, scratch);
     const float scale_a = 1.0f / sqrtf(sa / (float)width + eps);
     if (b == nullptr) {
-        for (int i = threadIdx.x; i < width; i += 256)
-            dst[i] = from_f32<TX>(to_f32<TX>(dst[i]) + mult * (to_f32<TA>(ra[i]) * scale_a * to_f32<W>(w[i])));
+        for (int i = threadIdx.x; i < width; i += 256) {
+            const TX next = from_f32<TX>(to_f32<TX>(dst[i]) + mult * (to_f32<TA>(ra[i]) * scale_a * to_f32<W>(w[i])));
+            dst[i] = next;
+            if (copy != nullptr) copy[i] = from_f32<bf16>(to_f32<TX>(next));
+        }
         return;
     }
     const TA* rb = b + (size_t)blockIdx.x * width;
@@ -193,13 +199,16 @@ rms_join_kernel(TX* __restrict__ x, const TA* __restrict__ a, const W* __restric
     }
     sy = block_sum(sy, scratch);
     const float scale_y = 1.0f / sqrtf(sy / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += 256)         // a thread reads back what it wrote itself
-        dst[i] = from_f32<TX>(to_f32<TX>(dst[i]) + mult * (y[i] * scale_y * to_f32<W>(w[i])));
+    for (int i = threadIdx.x; i < width; i += 256) {       // a thread reads back what it wrote itself
+        const TX next = from_f32<TX>(to_f32<TX>(dst[i]) + mult * (y[i] * scale_y * to_f32<W>(w[i])));
+        dst[i] = next;
+        if (copy != nullptr) copy[i] = from_f32<bf16>(to_f32<TX>(next));
+    }
 }
 
 extern "C" int qil_rms_join(void* x, int x_dtype, const void* a, const void* wa, const void* b, const void* wb,
                             int branch_dtype, const void* w, int weight_dtype, int n_rows, int width, float eps,
-                            float pre, float mult, cudaStream_t stream) {
+                            float pre, float mult, void* rows, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (width <= 0 || width > 40960) QIL_REFUSE("rms_join: width %d", width);
     if (b != nullptr && (wa == nullptr || wb == nullptr)) QIL_REFUSE("rms_join: two branches need a weight each");
@@ -212,7 +221,7 @@ extern "C" int qil_rms_join(void* x, int x_dtype, const void* a, const void* wa,
         if (err == cudaSuccess)                                                                                   \
             qil_launch_chained(rms_join_kernel<TX, TA, WT>, dim3(n_rows), dim3(256), smem, stream, (TX*)x,        \
                                (const TA*)a, (const WT*)wa, (const TA*)b, (const WT*)wb, (const WT*)w, width, eps, \
-                               pre, mult);                                                                        \
+                               pre, mult, (bf16*)rows);                                                           \
     } while (0)
 #define QIL_JOIN_W(TX, TA)                                                                                        \
     do {                                                                                                          \

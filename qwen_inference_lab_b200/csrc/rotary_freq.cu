@@ -17,7 +17,8 @@
 // [H][d plain, r rotated] and one row [c latent, r rotated key part].  The latent is divided by its root mean
 // square and multiplied by a weight (float32), the key part and every query's rotated part are rotated.  The
 // page row of the token becomes the key [c normed latent, r rotated key part] and the value [c normed latent,
-// zeros up to value_width]; the rotated query parts go to columns c .. c + r of every head's row of q_att
+// zeros up to value_width] (value_width 0: the page holds key rows only, the value being the key's first c
+// columns); the rotated query parts go to columns c .. c + r of every head's row of q_att
 // [N][H][c + r] (the first c columns receive the query folded through the key expansion, by another kernel).
 #include "common.cuh"
 
@@ -41,14 +42,28 @@ __device__ __forceinline__ float rotated_element(const float* __restrict__ vec, 
     return j == first ? u * c - v * s : v * c + u * s;
 }
 
+// V = 16 / sizeof(T) elements after rotation, from element j0 of a head on, as one 16-byte store.
+template <typename T>
+__device__ __forceinline__ void store_rotated16(T* __restrict__ dst, const float* __restrict__ head_vals, int j0, int rot_dims,
+                                                int layout, const float* __restrict__ table) {
+    constexpr int V = 16 / (int)sizeof(T);
+    uint4 packed;
+    T* out = reinterpret_cast<T*>(&packed);
+#pragma unroll
+    for (int k = 0; k < V; ++k) out[k] = from_f32<T>(rotated_element(head_vals, j0 + k, rot_dims, layout, table));
+    *reinterpret_cast<uint4*>(dst) = packed;
+}
+
+// `wide`: every row, column and head starts on a 16-byte boundary, so loads and stores move 16 bytes each.
 template <typename T, typename W>
 __global__ void __launch_bounds__(256)
 qk_rotate_store_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col, int v_col, T* __restrict__ q_out,
                        T* __restrict__ pages, const W* __restrict__ q_norm_w, const W* __restrict__ k_norm_w, float eps,
                        const float* __restrict__ freq, int rot_dims, int layout, const int* __restrict__ positions,
                        const int* __restrict__ token_row, const int* __restrict__ block_table, int table_stride,
-                       int n_q_heads, int n_kv_heads, int d, int e, int page_size, int num_pages) {
-    extern __shared__ float vals[];          // [Hq * d + Hkv * d]: q then k, normed, float32;  then [rot_dims]: the angles
+                       int n_q_heads, int n_kv_heads, int d, int e, int page_size, int num_pages, int wide) {
+    constexpr int V = 16 / (int)sizeof(T);
+    extern __shared__ __align__(16) float vals[];   // [Hq * d + Hkv * d]: q then k, normed, float32;  then [rot_dims]: the angles
     __shared__ float scratch[32];
     qil_wait_for_producer();
     qil_release_consumer();
@@ -59,8 +74,21 @@ qk_rotate_store_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col,
     const float* table = vals + q_width + k_width;
     angle_table(vals + q_width + k_width, rot_dims, pos, freq);
     float sq = 0.f, sk = 0.f;
-    for (int i = tid; i < q_width; i += 256) { const float x = to_f32<T>(row[q_col + i]); vals[i] = x; sq = fmaf(x, x, sq); }
-    for (int i = tid; i < k_width; i += 256) { const float x = to_f32<T>(row[k_col + i]); vals[q_width + i] = x; sk = fmaf(x, x, sk); }
+    if (wide) {
+        auto load = [&](int column, int width, float* dst, float& sum) {
+            for (int c = tid; c < width / V; c += 256) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(row + column + c * V);
+                const T* x = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int k = 0; k < V; ++k) { const float f = to_f32<T>(x[k]); dst[c * V + k] = f; sum = fmaf(f, f, sum); }
+            }
+        };
+        load(q_col, q_width, vals, sq);
+        load(k_col, k_width, vals + q_width, sk);
+    } else {
+        for (int i = tid; i < q_width; i += 256) { const float x = to_f32<T>(row[q_col + i]); vals[i] = x; sq = fmaf(x, x, sq); }
+        for (int i = tid; i < k_width; i += 256) { const float x = to_f32<T>(row[k_col + i]); vals[q_width + i] = x; sk = fmaf(x, x, sk); }
+    }
     if (q_norm_w != nullptr) {
         sq = block_sum(sq, scratch);
         sk = block_sum(sk, scratch);
@@ -71,9 +99,16 @@ qk_rotate_store_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col,
     }
     __syncthreads();
     T* q_dst = q_out + (size_t)token * q_width;
-    for (int i = tid; i < q_width; i += 256) {
-        const int head = i / d, j = i - head * d;
-        q_dst[i] = from_f32<T>(rotated_element(vals + head * d, j, rot_dims, layout, table));
+    if (wide) {
+        for (int c = tid; c < q_width / V; c += 256) {
+            const int head = c * V / d, j = c * V - head * d;
+            store_rotated16<T>(q_dst + c * V, vals + head * d, j, rot_dims, layout, table);
+        }
+    } else {
+        for (int i = tid; i < q_width; i += 256) {
+            const int head = i / d, j = i - head * d;
+            q_dst[i] = from_f32<T>(rotated_element(vals + head * d, j, rot_dims, layout, table));
+        }
     }
     if (n_kv_heads == 0) return;
     const int index = pos / page_size;
@@ -81,6 +116,20 @@ qk_rotate_store_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col,
     if (page < 0 || page >= num_pages) return;      // never write outside the pool
     const int slot = pos % page_size;
     T* page_base = pages + (size_t)page * n_kv_heads * page_size * (d + e);
+    if (wide) {
+        for (int c = tid; c < k_width / V; c += 256) {
+            const int head = c * V / d, j = c * V - head * d;
+            store_rotated16<T>(page_base + ((size_t)head * page_size + slot) * d + j, vals + q_width + head * d, j, rot_dims,
+                               layout, table);
+        }
+        T* values = page_base + (size_t)n_kv_heads * page_size * d;
+        for (int c = tid; c < v_width / V; c += 256) {
+            const int head = c * V / e, j = c * V - head * e;
+            *reinterpret_cast<uint4*>(values + ((size_t)head * page_size + slot) * e + j) =
+                *reinterpret_cast<const uint4*>(row + v_col + c * V);
+        }
+        return;
+    }
     for (int i = tid; i < k_width; i += 256) {
         const int head = i / d, j = i - head * d;
         page_base[((size_t)head * page_size + slot) * d + j] =
@@ -109,13 +158,16 @@ extern "C" int qil_qk_rotate_store(const void* proj, int ld, int q_col, int k_co
     if (smem > 160 * 1024) QIL_REFUSE("qk_rotate_store: %d values of q and k per token are too many", (n_q_heads + n_kv_heads) * d);
     cudaError_t err = cudaSuccess;
     QIL_DISPATCH_2(act_dtype, norm_dtype, {
+        constexpr int V = 16 / (int)sizeof(T);
+        const int wide = (d % V == 0 && e % V == 0 && ld % V == 0 && q_col % V == 0 && k_col % V == 0 && v_col % V == 0 &&
+                          (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)pages) & 15) == 0) ? 1 : 0;
         if (smem > 48 * 1024)
             err = cudaFuncSetAttribute(qk_rotate_store_kernel<T, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err == cudaSuccess)
             qil_launch_chained(qk_rotate_store_kernel<T, W>, dim3(n_tokens), dim3(256), smem, stream,
                                (const T*)proj, ld, q_col, k_col, v_col, (T*)q_out, (T*)pages, (const W*)q_norm_w,
                                (const W*)k_norm_w, eps, freq, rot_dims, layout, positions, token_row, block_table,
-                               table_stride, n_q_heads, n_kv_heads, d, e, page_size, num_pages);
+                               table_stride, n_q_heads, n_kv_heads, d, e, page_size, num_pages, wide);
     });
     if (err != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(err)); return (int)err; }
     QIL_CHECK_LAUNCH();
@@ -166,7 +218,7 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_col, int kv_col,
         if (i < c) {
             const T z = from_f32<T>(vals[i] * scale * to_f32<W>(norm_w[i]));
             key[i] = z;
-            value[i] = z;
+            if (value_width > 0) value[i] = z;
         } else {
             key[i] = from_f32<T>(rotated_element(vals + c, i - c, rot_dims, layout, table));
         }
@@ -180,7 +232,7 @@ extern "C" int qil_latent_prepare(const void* proj, int ld, int q_col, int kv_co
                                   int n_tokens, int n_heads, int d, int r, int c, int value_width, int page_size,
                                   int num_pages, int act_dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (n_heads <= 0 || d <= 0 || r < 0 || c <= 0 || page_size <= 0 || value_width < c || value_width > c + r)
+    if (n_heads <= 0 || d <= 0 || r < 0 || c <= 0 || page_size <= 0 || (value_width != 0 && (value_width < c || value_width > c + r)))
         QIL_REFUSE("latent_prepare: heads %d sizes %d/%d latent %d values %d page %d", n_heads, d, r, c, value_width, page_size);
     if (rot_dims < 0 || rot_dims > r || (rot_dims & 1) || (rot_dims > 0 && freq == nullptr) || (layout != 0 && layout != 1))
         QIL_REFUSE("latent_prepare: %d rotated dimensions of %d, layout %d", rot_dims, r, layout);

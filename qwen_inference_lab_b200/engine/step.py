@@ -305,16 +305,20 @@ class StepRunner:
             graphs = []
             stream = torch.cuda.Stream()
             stream.wait_stream(torch.cuda.current_stream())
+            # "relaxed": calls that CUDA forbids while any stream records only because they might touch the
+            # recording (an event query by the pinned-memory allocator about a copy of an earlier step, an
+            # allocation) do not end it; what really waits on the recording stream fails as before
+            mode = dict(pool=self._graph_pool, capture_error_mode="relaxed")
             with torch.cuda.stream(stream):
                 current = torch.cuda.CUDAGraph()
-                current.capture_begin(pool=self._graph_pool)
+                current.capture_begin(**mode)
 
                 def cut():
                     nonlocal current
                     current.capture_end()
                     graphs.append(current)
                     current = torch.cuda.CUDAGraph()
-                    current.capture_begin(pool=self._graph_pool)
+                    current.capture_begin(**mode)
 
                 try:
                     logits = self.model.forward(ctx, self.views, logit_rows, checkpoint=cut)

@@ -93,13 +93,14 @@ def library(head_dim):
 _sm_count = None
 
 
-def _slots(head_dim) -> int:
-    """Blocks of the span kernel that run at a time: SMs x blocks per SM (shared memory decides)."""
+def _slots(head_dim, planes=2) -> int:
+    """Blocks of the span kernel that run at a time: SMs x blocks per SM (shared memory decides; ``planes`` = 1:
+    pages of one row per position, half the tiles)."""
     global _sm_count
     if _sm_count is None:
         _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count \
             if torch.cuda.is_available() else 148
-    block_smem = (16 + 4 * KV_TILE) * (head_dim + 8) * 2 + 2048
+    block_smem = (16 + 2 * planes * KV_TILE) * (head_dim + 8) * 2 + 2048
     return _sm_count * max(1, min(3, (227 * 1024) // block_smem))
 
 
@@ -226,12 +227,21 @@ class ScoreOptions:
 
 
 def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_heads, head_dim, page_size, window,
-            scale, slopes_log2=None, options=None):
+            scale, slopes_log2=None, options=None, shared_rows=False):
     """tile_info int32 [n_tiles * 4]: (first token, its position, rows <= 64, block-table row) per tile.
     ``slopes_log2`` float32 [Hq]: slope_h * log2(e) of a bias slope_h * (query position - key position) that is
-    taken off the scaled score.  ``options``: a :class:`ScoreOptions` (no window then)."""
+    taken off the scaled score.  ``options``: a :class:`ScoreOptions` (no window then).  ``shared_rows``: a page
+    holds one row per position, the key, whose leading columns are the value (no slopes or options then)."""
     lib = library(head_dim)
     _check_slopes(slopes_log2, n_q_heads)
+    if shared_rows:
+        if options or slopes_log2 is not None:
+            raise KernelError("attention: shared rows go without slopes and score options")
+        _check(lib, lib.qil_attn_prefill_shared(
+            _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), _p(block_table), c_int(block_table.shape[1]),
+            c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_int(window),
+            c_float(scale), _stream()), "attention (prompt portions)")
+        return
     if options:
         options.check(n_q_heads)
         if window:
@@ -248,14 +258,24 @@ def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_head
 
 
 def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_len, block_table,
-           n_q_heads, n_kv_heads, head_dim, page_size, window, scale, tickets=None, slopes_log2=None, options=None):
+           n_q_heads, n_kv_heads, head_dim, page_size, window, scale, tickets=None, slopes_log2=None, options=None,
+           shared_rows=False):
     """decode_info int32 [n_decode * 4]: (token, its position, block-table row, the step's longest context)
     per single token.  A negative ``span_len``: the kernels cut the step's longest context into ``n_spans``
     equal spans of at most ``-span_len`` positions (see ``plan_spans``).  ``tickets``: int32 zeros, one per
     (token, query head) or more (``decode_scratch``): the last block of a token's spans merges them; None: a
-    second kernel does."""
+    second kernel does.  ``shared_rows``: see ``prefill``."""
     lib = library(head_dim)
     _check_slopes(slopes_log2, n_q_heads)
+    if shared_rows:
+        if options or slopes_log2 is not None:
+            raise KernelError("attention: shared rows go without slopes and score options")
+        _check(lib, lib.qil_attn_decode_shared(
+            _p(q), _p(pages), _p(out), _p(decode_info), c_int(n_decode), _p(part_o), _p(part_ml), _p(tickets), c_int(n_spans),
+            c_int(span_len), _p(block_table), c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads),
+            c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), _stream()),
+            "attention (single tokens)", kernels=1 if tickets is not None else 2)
+        return
     if options:
         options.check(n_q_heads)
         if window:
@@ -316,32 +336,39 @@ def attend_projection(ctx, qkv, cache, out, n_q_heads, n_kv_heads, own_kv_heads,
         "attention (single tokens from the projection)", kernels=1 if tickets is not None else 2)
 
 
-def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, slopes_log2=None, options=None):
+def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, slopes_log2=None, options=None,
+           shared_rows=False):
     """q, out bfloat16 [N, Hq*D]; cache a KVCacheView whose pages already hold this step's keys and values.
-    ``slopes_log2``, ``options``: see ``prefill``."""
+    ``slopes_log2``, ``options``, ``shared_rows``: see ``prefill``."""
     if q.dtype != torch.bfloat16 or cache.pages.dtype != torch.bfloat16:
         raise KernelError("the tensor-core attention takes bfloat16 queries and pages")
-    if tuple(cache.pages.shape[1:]) != (2, n_kv_heads, cache.page_size, head_dim):
+    planes = 1 if shared_rows else 2
+    if tuple(cache.pages.shape[1:]) != (planes, n_kv_heads, cache.page_size, head_dim):
         raise KernelError(f"attention: cache layout {tuple(cache.pages.shape)}")
     arrays, counts = step_plan(ctx)
     n_tiles, n_big, n_rest, n_decode = (counts[name] // 4 for name in
                                         ("tile_info", "big_tile_info", "rest_tile_info", "decode_info"))
-    if n_big and not options and attention_tc.supports(head_dim, cache.page_size, window):
+    if n_big and (not options or attention_tc.takes(options)) and not shared_rows \
+            and attention_tc.supports(head_dim, cache.page_size, window):
         # whole 128-token tiles on tcgen05 with the accumulators in tensor memory, the leftovers below
+        if options:
+            options.check(n_q_heads)
         attention_tc.prefill(q, cache.pages, out, arrays["big_tile_info"], n_big, cache.block_table,
-                             n_q_heads, n_kv_heads, cache.page_size, scale, slopes_log2=slopes_log2)
+                             n_q_heads, n_kv_heads, cache.page_size, scale, slopes_log2=slopes_log2,
+                             chunk=options.chunk if options else 0, sink_log2=options._sink_log2 if options else None)
         if n_rest:
             prefill(q, cache.pages, out, arrays["rest_tile_info"], n_rest, cache.block_table, n_q_heads,
                     n_kv_heads, head_dim, cache.page_size, window, scale, slopes_log2, options)
     elif n_tiles:
         prefill(q, cache.pages, out, arrays["tile_info"], n_tiles, cache.block_table, n_q_heads, n_kv_heads,
-                head_dim, cache.page_size, window, scale, slopes_log2, options)
+                head_dim, cache.page_size, window, scale, slopes_log2, options, shared_rows)
     if n_decode:
         n_spans, longest_span = plan_spans(n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
-                                           getattr(ctx, "min_context", 0) or None)
+                                           getattr(ctx, "min_context", 0) or None,
+                                           slots=_slots(head_dim, planes) if shared_rows else None)
         part_o, part_ml, tickets = decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim)
         if not merge_in_kernel(n_decode, n_q_heads, n_kv_heads, head_dim):
             tickets = None
         decode(q, cache.pages, out, arrays["decode_info"], n_decode, part_o, part_ml, n_spans, -longest_span,
                cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale, tickets, slopes_log2,
-               options)
+               options, shared_rows)

@@ -34,12 +34,23 @@ def supports(head_dim, page_size, window) -> bool:
     return head_dim == HEAD_DIM and window == 0 and page_size in (8, 16, 32, 64)
 
 
+def takes(options) -> bool:
+    """Of the score options (``attention_mma.ScoreOptions``) this kernel has chunks and a learned sink."""
+    return not options.softcap and options.distance_bias is None and (not options.sink or options.sink_logits is not None)
+
+
 def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_heads, page_size, scale, trace=None,
-            lib=None, slopes_log2=None):
+            lib=None, slopes_log2=None, chunk=0, sink_log2=None):
     """q, out bfloat16 [N, Hq*128]; pages [num_pages, 2, Hkv, page_size, 128];
     tile_info int32 [n_tiles * 4] = (first token, its position, 128, block-table row).
     ``slopes_log2`` float32 [Hq] on the device: slope_h * log2(e) of a bias slope_h * (query position - key
-    position) taken off the scaled score."""
+    position) taken off the scaled score.  ``chunk`` > 0: a query sees the keys of its own chunk of that many
+    positions only.  ``sink_log2`` float32 [Hq] on the device: learned scores times log2(e) whose exponentials join
+    the softmax's denominator."""
+    if sink_log2 is not None:
+        _need(sink_log2, "sink_log2", torch.float32, 1)
+        if sink_log2.shape[0] != n_q_heads:
+            raise KernelError("attention_tc: one sink score per query head")
     if slopes_log2 is not None:
         _need(slopes_log2, "slopes_log2", torch.float32, 1)
         if slopes_log2.shape[0] != n_q_heads:
@@ -50,10 +61,11 @@ def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_head
     lib = lib or library()
     word = _fault.tensor(q.device)
     _fault.mark()
-    _check(lib, lib.qil_attn_tc_prefill_biased(
+    _check(lib, lib.qil_attn_tc_prefill_masked(
         _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), c_int(q.shape[0]), _p(block_table),
         c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]),
-        c_float(scale), _p(slopes_log2), _p(word), _p(trace), _stream()), "attention (128-token tiles)")
+        c_float(scale), _p(slopes_log2), c_int(int(chunk or 0)), _p(sink_log2), _p(word), _p(trace), _stream()),
+        "attention (128-token tiles)")
 
 
 def check(wait=True) -> None:

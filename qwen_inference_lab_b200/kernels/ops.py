@@ -379,10 +379,16 @@ def qk_norm_rope_store(qkv, q_out, kv_cache, q_norm_w, k_norm_w, eps, rope_table
     return q_out
 
 
-def check_pages(kv_cache, dtype, n_kv_heads, page_size, head_dim, v_dim, what):
+def check_pages(kv_cache, dtype, n_kv_heads, page_size, head_dim, v_dim, what, shared_rows=False):
     """One layer's pages: [pages, 2, kv_heads, page_size, head_dim] when keys and values have one size,
-    else [pages, kv_heads * page_size * (head_dim + v_dim)] (a page's key rows, then its value rows)."""
+    else [pages, kv_heads * page_size * (head_dim + v_dim)] (a page's key rows, then its value rows); with
+    ``shared_rows`` [pages, 1, kv_heads, page_size, head_dim] (the value is the key's first v_dim columns)."""
     _need(kv_cache, "kv_cache", dtype)
+    if shared_rows:
+        if tuple(kv_cache.shape[1:]) != (1, n_kv_heads, page_size, head_dim) or not 0 < v_dim <= head_dim:
+            raise KernelError(f"{what}: cache layout {tuple(kv_cache.shape)} for {n_kv_heads} shared rows of {head_dim} "
+                              f"(values of {v_dim}), pages of {page_size}")
+        return
     equal = tuple(kv_cache.shape[1:]) == (2, n_kv_heads, page_size, head_dim) and v_dim == head_dim
     flat = kv_cache.ndim == 2 and kv_cache.shape[1] == n_kv_heads * page_size * (head_dim + v_dim)
     if not (equal or flat):
@@ -392,10 +398,11 @@ def check_pages(kv_cache, dtype, n_kv_heads, page_size, head_dim, v_dim, what):
 
 def attention_generic(q, kv_cache, out, positions, token_row, block_table, n_q_heads, n_kv_heads,
                       head_dim, page_size, window, scale, v_dim=None, slopes=None, softcap=0.0, distance_bias=None,
-                      chunk=0, sink=False, sink_logits=None):
+                      chunk=0, sink=False, sink_logits=None, shared_rows=False):
     """Causal GQA attention of every token over its request's pages (CUDA cores, float32 math).
 
     ``v_dim``: the size of a value head when it differs from ``head_dim`` (out is then [N, Hq * v_dim]).
+    ``shared_rows``: a page holds one row per position, the key; its first ``v_dim`` columns are the value.
     ``slopes`` float32 [Hq]: score = q.k * scale - slopes[h] * (query position - key position).
     ``softcap``: score <- softcap * tanh(score / softcap) before any bias.  ``distance_bias`` float32
     [Hq, distances]: added by distance, the last entry for every distance beyond.  ``chunk``: a position sees
@@ -403,7 +410,7 @@ def attention_generic(q, kv_cache, out, positions, token_row, block_table, n_q_h
     ``sink_logits`` float32 [Hq]: exp(sink_logits[h]) is added instead (a learned score per head, not scaled)."""
     v_dim = head_dim if v_dim is None else int(v_dim)
     _need(q, "q", ndim=2); _need(out, "out", q.dtype, 2)
-    check_pages(kv_cache, q.dtype, n_kv_heads, page_size, head_dim, v_dim, "attention_generic")
+    check_pages(kv_cache, q.dtype, n_kv_heads, page_size, head_dim, v_dim, "attention_generic", shared_rows)
     n = q.shape[0]
     if q.shape[1] != n_q_heads * head_dim or out.shape != (n, n_q_heads * v_dim):
         raise KernelError("attention_generic: q/out shapes do not match the head counts")
@@ -427,7 +434,7 @@ def attention_generic(q, kv_cache, out, positions, token_row, block_table, n_q_h
         c_int(n), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(v_dim), c_int(page_size),
         c_int(kv_cache.shape[0]), c_int(window), c_float(scale), _p(slopes), c_float(softcap), _p(distance_bias),
         c_int(distance_bias.shape[1] if distance_bias is not None else 0), c_int(chunk), c_int(1 if sink else 0),
-        _p(sink_logits), c_int(dtype_code(q.dtype)), _stream()),
+        _p(sink_logits), c_int(1 if shared_rows else 0), c_int(dtype_code(q.dtype)), _stream()),
         "attention_generic")
     return out
 
@@ -746,10 +753,15 @@ def lin_norm_gate_whole(scratch, projected, gate_column, norm_weight, eps, out):
     return out
 
 
-def rms_join(x, a, weight, eps, mult=1.0, *, b=None, weight_a=None, weight_b=None, pre=0.5):
+def rms_join(x, a, weight, eps, mult=1.0, *, b=None, weight_a=None, weight_b=None, pre=0.5, rows=None):
     """x += mult * a / sqrt(mean(a^2) + eps) * weight, row by row in float32: a branch joins the stream ``x`` (float32
     or bfloat16 [N, width], updated in place) through a norm on the branch.  With a second branch ``b``:
-    y = pre * (rms(a) * weight_a + rms(b) * weight_b), x += mult * rms(y) * weight."""
+    y = pre * (rms(a) * weight_a + rms(b) * weight_b), x += mult * rms(y) * weight.  ``rows``: bfloat16 [N, width] that
+    receives the stream's new values rounded (what the next product reads, without a cast of its own)."""
+    if rows is not None:
+        _need(rows, "rows", torch.bfloat16, 2)
+        if rows.shape != x.shape:
+            raise KernelError("rms_join: the rounded copy has another shape")
     _need(x, "x", ndim=2); _need(a, "a", ndim=2); _need(weight, "weight", ndim=1)
     if a.shape != x.shape or weight.shape[0] != x.shape[1]:
         raise KernelError("rms_join: shapes differ")
@@ -760,7 +772,8 @@ def rms_join(x, a, weight, eps, mult=1.0, *, b=None, weight_a=None, weight_b=Non
     lib = core()
     _check(lib, lib.qil_rms_join(_p(x), c_int(dtype_code(x.dtype)), _p(a), _p(weight_a), _p(b), _p(weight_b),
                                  c_int(dtype_code(a.dtype)), _p(weight), c_int(dtype_code(weight.dtype)), c_int(x.shape[0]),
-                                 c_int(x.shape[1]), c_float(eps), c_float(pre), c_float(mult), _stream()), "rms_join")
+                                 c_int(x.shape[1]), c_float(eps), c_float(pre), c_float(mult), _p(rows), _stream()),
+           "rms_join")
     return x
 
 
@@ -830,8 +843,9 @@ def latent_prepare(proj, q_column, kv_column, q_att, kv_cache, norm_w, eps, freq
     """The tail of a latent attention's projection.  ``proj`` [N, width] holds the queries [H][plain_dim, rot_dim]
     from ``q_column`` on and one row [latent_dim, rot_dim] per token from ``kv_column`` on.  The latent is normed
     (root mean square, ``norm_w``), the shared key part and the queries' rotated parts are rotated; the token's page
-    row becomes key [latent, rotated part] and value [latent, zeros up to ``value_width``]; the rotated query parts
-    go to the last rot_dim columns of every head's row of ``q_att`` [N, H * (latent_dim + rot_dim)]."""
+    row becomes key [latent, rotated part] and value [latent, zeros up to ``value_width``] (``value_width`` 0: pages
+    of shared rows, which hold the key alone); the rotated query parts go to the last rot_dim columns of every
+    head's row of ``q_att`` [N, H * (latent_dim + rot_dim)]."""
     _need(proj, "proj", ndim=2); _need(q_att, "q_att", proj.dtype, 2); _need(norm_w, "norm_w", ndim=1)
     n, ld = proj.shape
     width = latent_dim + rot_dim
@@ -840,7 +854,7 @@ def latent_prepare(proj, q_column, kv_column, q_att, kv_cache, norm_w, eps, freq
         raise KernelError("latent_prepare: shapes do not fit together")
     _check_rotation(freq, rot_dims, layout, rot_dim, "latent_prepare")
     _need(positions, "positions", torch.int32, 1); _need(token_row, "token_row", torch.int32, 1)
-    check_pages(kv_cache, proj.dtype, 1, page_size, width, value_width, "latent_prepare")
+    check_pages(kv_cache, proj.dtype, 1, page_size, width, value_width or latent_dim, "latent_prepare", value_width == 0)
     _need(block_table, "block_table", torch.int32, 2)
     lib = core()
     _check(lib, lib.qil_latent_prepare(

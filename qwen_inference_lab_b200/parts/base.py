@@ -67,12 +67,15 @@ class KVCacheSpec:
     ``v_head_dim``: the size of a value head where it differs from a key head's (0: the same).
     ``chunk`` > 0 means that a position reads only the positions of its own chunk of that many
     (chunks counted from position 0), so pages of chunks that are over are given back as well.
+    ``shared_rows``: a position's value is the leading ``v_head_dim`` columns of its key (all of it when 0), so a
+    page holds one row per position and kv head and no value rows.
     """
     kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
     chunk: int = 0
+    shared_rows: bool = False
 
     @property
     def value_dim(self) -> int:

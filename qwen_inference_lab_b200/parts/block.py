@@ -95,7 +95,9 @@ class PostNormBlock(Part):
     """x <- x + mult * rms(mixer(x); w1), then x <- x + mult * rms(ff(x); w2): the sublayers read the residual
     stream itself (cast to the activation dtype when the stream is float32 under bfloat16 activations) and their
     output is normed (root mean square over the width, a weight per feature, float32) before it joins the stream.
-    The norm, the multiplier and the sum are one kernel (``kernels.ops.rms_join``).  A mixer that sets
+    The norm, the multiplier and the sum are one kernel (``kernels.ops.rms_join``), which under bfloat16 activations
+    also writes the float32 stream's new values rounded, for the next sublayer to read (the next block finds them
+    in ``ctx.extras``), so that only the first block of a step casts the stream.  A mixer that sets
     ``joins_stream`` is handed the stream, the weight and the multiplier and does the join itself (two mixers side
     by side fold their own output norms into that kernel).  ``feed_forward`` may be None; the second norm's weight
     is then optional.  names: (first norm's weight, second norm's weight)."""
@@ -119,14 +121,23 @@ class PostNormBlock(Part):
 
     def forward(self, ctx, x, cache):
         """x [N, width] is the residual stream; updated in place and returned."""
-        rows = x if x.dtype == ctx.dtype else ops.cast(x, ctx.dtype)
+        kept = ctx.extras.pop("stream_rows", None)          # (the stream, its rounded copy) of the block before
+        if x.dtype == ctx.dtype:
+            rows = x
+        else:
+            rows = kept[1] if kept is not None and kept[0] is x else ops.cast(x, ctx.dtype)
+        copies = x.dtype != ctx.dtype and ctx.dtype == torch.bfloat16
+        after = ctx.empty(x.shape) if copies else None
         if getattr(self.mixer, "joins_stream", False):
-            x = self.mixer.forward(ctx, rows, cache, stream=x, norm_weight=self.mixer_norm.data, mult=self.mult)
+            x = self.mixer.forward(ctx, rows, cache, stream=x, norm_weight=self.mixer_norm.data, mult=self.mult, rows=after)
         else:
             branch = self.mixer.forward(ctx, rows, cache, out_float32=True)
-            x = ops.rms_join(x, branch, self.mixer_norm.data, self.eps, self.mult)
-        if self.feed_forward is None:
-            return x
-        rows = x if x.dtype == ctx.dtype else ops.cast(x, ctx.dtype)
-        branch = self.feed_forward.forward(ctx, rows, out_float32=True)
-        return ops.rms_join(x, branch, self.ff_norm.data, self.eps, self.mult)
+            x = ops.rms_join(x, branch, self.mixer_norm.data, self.eps, self.mult, rows=after)
+        if self.feed_forward is not None:
+            rows = x if x.dtype == ctx.dtype else (after if copies else ops.cast(x, ctx.dtype))
+            branch = self.feed_forward.forward(ctx, rows, out_float32=True)
+            after = ctx.empty(x.shape) if copies else None
+            x = ops.rms_join(x, branch, self.ff_norm.data, self.eps, self.mult, rows=after)
+        if copies:
+            ctx.extras["stream_rows"] = (x, after)
+        return x

@@ -18,9 +18,11 @@ window; ``ops.head_product`` again (the sum through Wuv, times the gate); the ou
 than ``LIBRARY_ROWS`` tokens hands the two per-head products to the library as batched products over strided views
 of the same buffers (as ``Linear`` does with its products), and ``ops.head_gate`` applies the gates.
 
-A page holds the token's key row [z, rot(s)] and its value row.  Where c + r is a head size the tensor-core
-attention takes (a multiple of 16 up to 256), the value row is z followed by r zeros, so that keys and values
-have one size as that kernel wants; otherwise the value row is z alone and the float32 kernel runs.
+A page holds one row per token, the key [z, rot(s)]; the token's value z is that row's first c columns (the cache's
+shared rows), so the attention kernels fetch one tile per 64 positions and use it for the scores and for the
+weighted sum alike.  Where c + r is a head size the tensor-core attention takes (a multiple of 16 up to 256) a
+bfloat16 step runs there, and its output rows are c + r wide with the sums of the latents in their first c columns;
+otherwise, and in float32, the float32 kernel runs and gives rows of c.
 """
 from __future__ import annotations
 
@@ -50,7 +52,7 @@ class LatentAttention(Mixer):
             raise ValueError("latent attention rotates by frequencies, over at most its rotated dimensions")
         self.position = position
         self.key_width = self.latent_dim + self.rot_dim
-        # the value row's width: see the module's text
+        # the width of a bfloat16 step's attended rows: see the module's text
         self.value_width = self.key_width if attention_mma.supports(self.key_width, 1, 1) else self.latent_dim
         q_width = self.n_heads * (self.plain_dim + self.rot_dim)
         self.projection = StackedLinear(hidden_size, [(names["q"], q_width), (names["dkv"], self.key_width),
@@ -84,7 +86,7 @@ class LatentAttention(Mixer):
         return {**super().step_planners(), _PLANNER.key: _PLANNER}
 
     def cache_spec(self):
-        return KVCacheSpec(1, self.key_width, self.window, self.value_width if self.value_width != self.key_width else 0)
+        return KVCacheSpec(1, self.key_width, self.window, self.latent_dim, shared_rows=True)
 
     def forward(self, ctx, x, cache, residual=None, out_float32=False):
         """x [N, hidden] -> [N, hidden] (+ residual); ``cache`` is a KVCacheView of rows [latent, rotated key part]."""
@@ -106,8 +108,7 @@ class LatentAttention(Mixer):
         rotation = self.position
         ops.latent_prepare(projected, self.columns[0], self.columns[1], queries, cache.pages, self.latent_norm.data,
                            self.norm_eps, rotation.freq, rotation.rotary_dim, rotation.layout, ctx.positions, ctx.token_row,
-                           cache.block_table, heads, self.plain_dim, self.rot_dim, self.latent_dim, self.value_width,
-                           cache.page_size)
+                           cache.block_table, heads, self.plain_dim, self.rot_dim, self.latent_dim, 0, cache.page_size)
         if self._batched(projected):
             plain = projected[:, :self.columns[1]].unflatten(1, (heads, self.plain_dim + self.rot_dim))[:, :, :self.plain_dim]
             torch.bmm(plain.transpose(0, 1), self._query_fold.transpose(1, 2),
@@ -117,26 +118,29 @@ class LatentAttention(Mixer):
         return queries
 
     def attend(self, ctx, queries, cache):
-        """Every head over the one key row per token: [N, H * value_width] weighted sums of latents."""
+        """Every head over the one key row per token: per head a row whose first c columns are the weighted sum of
+        latents, [N, H * (c + r)] from the tensor-core kernels and [N, H * c] from the float32 kernel."""
         n, heads, width = queries.shape[0], self.n_heads, self.key_width
-        attended = ctx.empty((n, heads * self.value_width))
         if queries.dtype == torch.bfloat16 and self.value_width == width:
-            attention_mma.attend(ctx, queries, cache, attended, heads, 1, width, self.window, self.scale)
+            attended = ctx.empty((n, heads * width))
+            attention_mma.attend(ctx, queries, cache, attended, heads, 1, width, self.window, self.scale, shared_rows=True)
         else:
+            attended = ctx.empty((n, heads * self.latent_dim))
             ops.attention_generic(queries, cache.pages, attended, ctx.positions, ctx.token_row, cache.block_table, heads, 1,
-                                  width, cache.page_size, self.window, self.scale, v_dim=self.value_width)
+                                  width, cache.page_size, self.window, self.scale, v_dim=self.latent_dim, shared_rows=True)
         return attended
 
     def expand(self, ctx, attended, projected):
         """The weighted sums through Wuv, times the heads' gates: [N, H * e]."""
         n, heads = attended.shape[0], self.n_heads
+        stride = attended.shape[1] // heads          # c + r or c: see ``attend``
         mixed = ctx.empty((n, heads * self.value_dim))
         if self._batched(projected):
-            sums = attended.view(n, heads, self.value_width)[:, :, :self.latent_dim]
+            sums = attended.view(n, heads, stride)[:, :, :self.latent_dim]
             torch.bmm(sums.transpose(0, 1), self._value_unfold.transpose(1, 2),
                       out=mixed.view(n, heads, self.value_dim).transpose(0, 1))
             ops.head_gate(mixed, self.value_dim, projected, self.columns[2])
         else:
-            ops.head_product(attended, 0, self.value_width, self._value_unfold, mixed, 0, self.value_dim,
+            ops.head_product(attended, 0, stride, self._value_unfold, mixed, 0, self.value_dim,
                              gate=projected, gate_column=self.columns[2])
         return mixed

@@ -52,9 +52,10 @@ class ParallelMixers(Mixer):
         left, right = cache[:n_left], cache[n_left:]
         return (left if n_left > 1 else left[0]), (right if self._counts[1] > 1 else right[0])
 
-    def forward(self, ctx, x, cache, stream=None, norm_weight=None, mult=1.0, out_float32=True):
+    def forward(self, ctx, x, cache, stream=None, norm_weight=None, mult=1.0, out_float32=True, rows=None):
         """x [N, hidden] -> y float32 [N, hidden]; with ``stream`` (the residual stream, updated in place and
-        returned): stream += mult * rms(y) * norm_weight."""
+        returned): stream += mult * rms(y) * norm_weight, and ``rows`` (bfloat16, optional) receives the stream's
+        new values rounded."""
         left_view, right_view = self._views(cache)
         a = self.left.forward(ctx, x, left_view, out_float32=True)
         b = self.right.forward(ctx, x, right_view, out_float32=True)
@@ -67,4 +68,4 @@ class ParallelMixers(Mixer):
         if norm_weight.dtype != self.left_weight.data.dtype:
             norm_weight = norm_weight.to(self.left_weight.data.dtype)
         return ops.rms_join(stream, a, norm_weight, self.norm_eps, mult, b=b, weight_a=self.left_weight.data,
-                            weight_b=self.right_weight.data, pre=self.share)
+                            weight_b=self.right_weight.data, pre=self.share, rows=rows)

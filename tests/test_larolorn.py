@@ -44,18 +44,20 @@ def test_every_layer_run_has_a_cache_of_its_own():
     model = registry.lookup(cases.CASE_A).build(LarolornConfig.from_dict(cases.CASE_A))
     specs = model.cache_specs()
     assert len(specs) == 5
-    # the latent layers keep one row [latent, rotated key part] per token, inside a window of 20
-    assert specs[0] == specs[2] == KVCacheSpec(1, 32, 20, 0)
+    # the latent layers keep one row [latent, rotated key part] per token, inside a window of 20; the value is
+    # the row's first 24 columns and has no row of its own
+    assert specs[0] == specs[2] == KVCacheSpec(1, 32, 20, 24, shared_rows=True)
     # the parallel layers keep pages for the chunked attention and a float32 matrix per recurrent head
     assert specs[1] == specs[4] == (KVCacheSpec(2, 32, 0, 0, chunk=24), StateSpec((2, 16, 24), torch.float32))
     assert specs[3] == (KVCacheSpec(3, 16, 0, 8, chunk=7), StateSpec((3, 40, 8), torch.float32))
     cache = CacheManager(specs, num_pages=8, page_size=4, max_requests=2, max_context=64, dtype=torch.float32, device="cpu")
     views = cache.views()
-    assert views[0].pages.data_ptr() != views[2].pages.data_ptr()
+    assert views[0].pages.data_ptr() != views[2].pages.data_ptr() and tuple(views[0].pages.shape) == (8, 1, 1, 4, 32)
     assert views[1][1].slots.data_ptr() != views[4][1].slots.data_ptr()
-    # a key row that no tensor-core kernel takes keeps a value row of the latent alone
+    # whatever the key row's size: one row per token
     model = registry.lookup(cases.CASE_B).build(LarolornConfig.from_dict(cases.CASE_B))
-    assert model.cache_specs()[2] == KVCacheSpec(1, 14, 1, 10) and model.cache_specs()[1] == KVCacheSpec(1, 64, 33, 0)
+    assert model.cache_specs()[2] == KVCacheSpec(1, 14, 1, 10, shared_rows=True)
+    assert model.cache_specs()[1] == KVCacheSpec(1, 64, 33, 48, shared_rows=True)
 
 
 def _changed(change, case=cases.CASE_A):

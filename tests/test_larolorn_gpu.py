@@ -79,6 +79,13 @@ def test_a_normed_branch_joins_the_stream(width):
         out = ops.rms_join(stream.clone().cuda(), a.cuda(), w.cuda(), eps, 0.3, b=b.cuda(), weight_a=wa.cuda(), weight_b=wb.cuda(), pre=0.5)
         y = 0.5 * (plain.rms_norm(a.double(), wa, eps) + plain.rms_norm(b.double(), wb, eps))
         torch.testing.assert_close(out.cpu(), (stream.double() + 0.3 * plain.rms_norm(y, w, eps)).float(), atol=1e-5, rtol=1e-6)
+        # the rounded copy for the next product is the new stream rounded once, bit for bit, from either form
+        for two in (False, True):
+            copy = torch.full((5, width), float("nan"), dtype=torch.bfloat16, device="cuda")
+            more = dict(b=b.cuda(), weight_a=wa.cuda(), weight_b=wb.cuda(), pre=0.5) if two else {}
+            again = ops.rms_join(stream.clone().cuda(), a.cuda(), w.cuda(), eps, 0.3, rows=copy, **more)
+            assert torch.equal(copy, again.to(torch.bfloat16))
+            assert two or torch.equal(again, ops.rms_join(stream.clone().cuda(), a.cuda(), w.cuda(), eps, 0.3))
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
@@ -224,6 +231,29 @@ def test_chunked_attention_with_whole_norms_and_sinks_whole_cut_and_side_by_side
         got = through_the_step_function(part, 72, dtype, inputs, cuts, num_pages=48)
         for rid in inputs:
             close(got[rid], expected[rid], dtype)
+
+
+@pytest.mark.parametrize("chunk", [50, 128, 200, 4096])
+def test_whole_tiles_of_heads_of_128_take_the_tensor_memory_kernel_with_chunks_and_sinks(monkeypatch, chunk):
+    """Whole 128-token tiles of a prompt go to the tcgen05 kernel, which starts at the chunk of a tile's first row and
+    masks, row by row, what lies before a later row's chunk (chunk edges inside a tile, at a tile's edge, one edge in
+    the prompt, none); the sink's score joins every row's denominator.  Leftovers and single tokens take the tiled
+    kernels."""
+    from qwen_inference_lab_b200.kernels import attention_tc
+    calls = []
+    original = attention_tc.prefill
+    monkeypatch.setattr(attention_tc, "prefill",
+                        lambda *a, **k: (calls.append((k.get("chunk"), k.get("sink_log2") is not None)), original(*a, **k))[1])
+    m = cases.left(4, 2, 128, 128, 0.09, 10000.0, 128, chunk)
+    part = left_part(64, m)
+    w = fill(part, 31, torch.bfloat16)
+    inputs = {"a": rows(330, 64, 32), "b": rows(140, 64, 33)}
+    expected = {rid: plain.chunk_attention_mixer(x.double(), w, "m.", m, 1e-5, torch.bfloat16) for rid, x in inputs.items()}
+    for cuts in ({"a": [330], "b": [140]}, {"a": [129, 1, 200], "b": [7, 133]}):
+        got = through_the_step_function(part, 64, torch.bfloat16, inputs, cuts, page_size=16, num_pages=40)
+        for rid in inputs:
+            close(got[rid], expected[rid], torch.bfloat16)
+    assert calls and all(call == (chunk, True) for call in calls)
 
 
 def test_the_sink_takes_its_share_and_is_not_scaled():
