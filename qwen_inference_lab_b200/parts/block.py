@@ -97,7 +97,8 @@ class PostNormBlock(Part):
     output is normed (root mean square over the width, a weight per feature, float32) before it joins the stream.
     The norm, the multiplier and the sum are one kernel (``kernels.ops.rms_join``), which under bfloat16 activations
     also writes the float32 stream's new values rounded, for the next sublayer to read (the next block finds them
-    in ``ctx.extras``), so that only the first block of a step casts the stream.  A mixer that sets
+    in ``ctx.extras["stream_rows"]`` as (the stream, its copy); a part that changes the stream between two such blocks
+    has to remove that entry), so that only the first block of a step casts the stream.  A mixer that sets
     ``joins_stream`` is handed the stream, the weight and the multiplier and does the join itself (two mixers side
     by side fold their own output norms into that kernel).  ``feed_forward`` may be None; the second norm's weight
     is then optional.  names: (first norm's weight, second norm's weight)."""
