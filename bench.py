@@ -952,7 +952,7 @@ def _larolorn_kernels(torch, larolorn, virulix, sizes, pk, tokens_n, batch, cont
         q = x[:, :H * row].contiguous()
         return bench.timed(lambda: latent.attend(ctx, q, view))
     bench.measure(f"larolorn latent attention (one key row of {row} for {H} heads, window)", latent, H * row, latent_attention,
-                  (4.0 * H * row * pairs_window, None), batch * min(context + 1, span) * 2 * row * 2)
+                  (2.0 * H * (row + latent.latent_dim) * pairs_window, None), batch * min(context + 1, span) * row * 2)
     def grouped_attention(mixer):
         def kernel(ctx, x, view):
             q = x[:, :H * d].contiguous()

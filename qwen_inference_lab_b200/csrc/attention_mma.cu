@@ -97,6 +97,9 @@ struct AttnParams {
     // row per (kv head, slot), which is the key, and whose leading columns are the value: no value row is stored
     // or read, the value tile is the key tile, and the output's trailing columns hold sums the caller ignores
     int planes;
+    // how many leading columns of a value row anyone reads (D, or with shared rows the value's width rounded up to
+    // 16): the weighted sum is not computed for the rest, whose output columns stay zero
+    int v_cols;
     float scale_log2;         // head_dim^-1/2 * log2(e)
     // null, or one slope per query head, times log2(e): score = q.k * scale - slope_h * (query position - key position)
     const float* slopes_log2;
@@ -334,6 +337,7 @@ __device__ __forceinline__ void attn_prefill_tile(const AttnParams& p, const int
             a[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
 #pragma unroll
             for (int dp = 0; dp < D / 16; ++dp) {
+                if (dp * 16 >= p.v_cols) continue;      // the same for all threads; the loop stays unrolled
                 unsigned b0, b1, b2, b3;
                 ldmatrix_x4_trans(b0, b1, b2, b3,
                                   tV + (kt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + dp * 16 + (lane >> 4) * 8);
@@ -752,6 +756,7 @@ __device__ __forceinline__ void attn_decode_span_block(
         __syncwarp();
 #pragma unroll
         for (int dp = 0; dp < D / 16; ++dp) {
+            if (dp * 16 >= p.v_cols) continue;
             unsigned b0, b1, b2, b3;
             ldmatrix_x4_trans(b0, b1, b2, b3, tV + (((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + dp * 16 + (lane >> 4) * 8);
             mma_bf16(o[2 * dp], a, b0, b1);
@@ -881,7 +886,7 @@ static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, 
     p.q = (const bf16*)q; p.kv = (const bf16*)kv; p.out = (bf16*)out;
     p.block_table = block_table; p.table_stride = table_stride;
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
-    p.window = window; p.planes = 2;
+    p.window = window; p.planes = 2; p.v_cols = D;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.slopes_log2 = nullptr;
     p.scale = scale; p.softcap = 0.f; p.tanh_arg = p.cap_log2 = 0.f; p.dist_bias = nullptr; p.dist_len = 0; p.chunk = 0; p.sink = 0; p.sink_log2 = nullptr;
@@ -950,13 +955,15 @@ static int launch_prefill(const void* q, const void* kv, void* out, const int* t
                           const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                           int page_size, int num_pages, int window, float scale,
                           const float* slopes_log2, float softcap, const float* dist_bias, int dist_len, int chunk,
-                          int sink, cudaStream_t stream, const float* sink_log2 = nullptr, int planes = 2) {
+                          int sink, cudaStream_t stream, const float* sink_log2 = nullptr, int planes = 2, int v_cols = 0) {
     if (n_tiles <= 0) return 0;
     AttnParams p;
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
     if (planes != 1 && planes != 2) QIL_REFUSE("attention: a page holds 1 or 2 rows per position, not %d", planes);
+    if (v_cols < 0 || v_cols > D) QIL_REFUSE("attention: %d value columns of %d", v_cols, D);
     p.planes = planes;
+    if (v_cols > 0) p.v_cols = (v_cols + 15) / 16 * 16;
     p.slopes_log2 = slopes_log2;
     if (fill_options(p, softcap, dist_bias, dist_len, chunk, sink, sink_log2)) return -1;
     if (n_tiles > 65535) QIL_REFUSE("attention: %d query tiles in one launch; at most 65535", n_tiles);
@@ -994,13 +1001,14 @@ extern "C" int qil_attn_prefill_modified(const void* q, const void* kv, void* ou
                           num_pages, 0, scale, slopes_log2, softcap, dist_bias, dist_len, chunk, sink, stream, sink_log2);
 }
 
-// The same over pages of one row per position (shared rows, see AttnParams): out's columns past the value's width
-// hold weighted sums of the rows' other columns.
+// The same over pages of one row per position (shared rows, see AttnParams); value_cols: the value's width (0: all of
+// the row): out's columns past it, rounded up to 16, are zero.
 extern "C" int qil_attn_prefill_shared(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
                                        const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
-                                       int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
+                                       int page_size, int num_pages, int window, float scale, int value_cols,
+                                       cudaStream_t stream) {
     return launch_prefill(q, kv, out, tile_info, n_tiles, block_table, table_stride, n_q_heads, n_kv_heads, page_size,
-                          num_pages, window, scale, nullptr, 0.f, nullptr, 0, 0, 0, stream, nullptr, 1);
+                          num_pages, window, scale, nullptr, 0.f, nullptr, 0, 0, 0, stream, nullptr, 1, value_cols);
 }
 
 extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
@@ -1025,14 +1033,16 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
                          int page_size, int num_pages, int window, float scale, const DecodeTail& tail,
                          cudaStream_t stream, const float* slopes_log2 = nullptr, float softcap = 0.f,
                          const float* dist_bias = nullptr, int dist_len = 0, int chunk = 0, int sink = 0,
-                         const float* sink_log2 = nullptr, int planes = 2) {
+                         const float* sink_log2 = nullptr, int planes = 2, int v_cols = 0) {
     if (n_decode <= 0) return 0;
     AttnParams p;
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
     if (planes != 1 && planes != 2) QIL_REFUSE("attention: a page holds 1 or 2 rows per position, not %d", planes);
     if (planes == 1 && tail.qkv != nullptr) QIL_REFUSE("attention: the projection's tail writes value rows; shared rows have none");
+    if (v_cols < 0 || v_cols > D) QIL_REFUSE("attention: %d value columns of %d", v_cols, D);
     p.planes = planes;
+    if (v_cols > 0) p.v_cols = (v_cols + 15) / 16 * 16;
     p.slopes_log2 = slopes_log2;
     if (fill_options(p, softcap, dist_bias, dist_len, chunk, sink, sink_log2)) return -1;
     if (check_decode_span(span_len, n_spans)) return -1;
@@ -1072,11 +1082,12 @@ extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const i
 extern "C" int qil_attn_decode_shared(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
                                       float* part_o, float* part_ml, unsigned* tickets, int n_spans, int span_len,
                                       const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
-                                      int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
+                                      int page_size, int num_pages, int window, float scale, int value_cols,
+                                      cudaStream_t stream) {
     DecodeTail none = {};
     return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, tickets, n_spans, span_len, block_table,
                          table_stride, n_q_heads, n_kv_heads, page_size, num_pages, window, scale, none, stream,
-                         nullptr, 0.f, nullptr, 0, 0, 0, nullptr, 1);
+                         nullptr, 0.f, nullptr, 0, 0, 0, nullptr, 1, value_cols);
 }
 
 // The same with a distance bias per query head (slopes_log2: float32 [n_q_heads], see AttnParams).

@@ -227,11 +227,12 @@ class ScoreOptions:
 
 
 def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_heads, head_dim, page_size, window,
-            scale, slopes_log2=None, options=None, shared_rows=False):
+            scale, slopes_log2=None, options=None, shared_rows=False, value_cols=0):
     """tile_info int32 [n_tiles * 4]: (first token, its position, rows <= 64, block-table row) per tile.
     ``slopes_log2`` float32 [Hq]: slope_h * log2(e) of a bias slope_h * (query position - key position) that is
     taken off the scaled score.  ``options``: a :class:`ScoreOptions` (no window then).  ``shared_rows``: a page
-    holds one row per position, the key, whose leading columns are the value (no slopes or options then)."""
+    holds one row per position, the key, whose leading ``value_cols`` columns (0: all) are the value (no slopes or
+    options then); the output's columns past those are zero."""
     lib = library(head_dim)
     _check_slopes(slopes_log2, n_q_heads)
     if shared_rows:
@@ -240,7 +241,7 @@ def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_head
         _check(lib, lib.qil_attn_prefill_shared(
             _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), _p(block_table), c_int(block_table.shape[1]),
             c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_int(window),
-            c_float(scale), _stream()), "attention (prompt portions)")
+            c_float(scale), c_int(int(value_cols)), _stream()), "attention (prompt portions)")
         return
     if options:
         options.check(n_q_heads)
@@ -259,7 +260,7 @@ def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_head
 
 def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_len, block_table,
            n_q_heads, n_kv_heads, head_dim, page_size, window, scale, tickets=None, slopes_log2=None, options=None,
-           shared_rows=False):
+           shared_rows=False, value_cols=0):
     """decode_info int32 [n_decode * 4]: (token, its position, block-table row, the step's longest context)
     per single token.  A negative ``span_len``: the kernels cut the step's longest context into ``n_spans``
     equal spans of at most ``-span_len`` positions (see ``plan_spans``).  ``tickets``: int32 zeros, one per
@@ -273,7 +274,7 @@ def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_
         _check(lib, lib.qil_attn_decode_shared(
             _p(q), _p(pages), _p(out), _p(decode_info), c_int(n_decode), _p(part_o), _p(part_ml), _p(tickets), c_int(n_spans),
             c_int(span_len), _p(block_table), c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads),
-            c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), _stream()),
+            c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), c_int(int(value_cols)), _stream()),
             "attention (single tokens)", kernels=1 if tickets is not None else 2)
         return
     if options:
@@ -337,9 +338,9 @@ def attend_projection(ctx, qkv, cache, out, n_q_heads, n_kv_heads, own_kv_heads,
 
 
 def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, slopes_log2=None, options=None,
-           shared_rows=False):
+           shared_rows=False, value_cols=0):
     """q, out bfloat16 [N, Hq*D]; cache a KVCacheView whose pages already hold this step's keys and values.
-    ``slopes_log2``, ``options``, ``shared_rows``: see ``prefill``."""
+    ``slopes_log2``, ``options``, ``shared_rows``, ``value_cols``: see ``prefill``."""
     if q.dtype != torch.bfloat16 or cache.pages.dtype != torch.bfloat16:
         raise KernelError("the tensor-core attention takes bfloat16 queries and pages")
     planes = 1 if shared_rows else 2
@@ -361,7 +362,7 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, s
                     n_kv_heads, head_dim, cache.page_size, window, scale, slopes_log2, options)
     elif n_tiles:
         prefill(q, cache.pages, out, arrays["tile_info"], n_tiles, cache.block_table, n_q_heads, n_kv_heads,
-                head_dim, cache.page_size, window, scale, slopes_log2, options, shared_rows)
+                head_dim, cache.page_size, window, scale, slopes_log2, options, shared_rows, value_cols)
     if n_decode:
         n_spans, longest_span = plan_spans(n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
                                            getattr(ctx, "min_context", 0) or None,
@@ -371,4 +372,4 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, s
             tickets = None
         decode(q, cache.pages, out, arrays["decode_info"], n_decode, part_o, part_ml, n_spans, -longest_span,
                cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale, tickets, slopes_log2,
-               options, shared_rows)
+               options, shared_rows, value_cols)

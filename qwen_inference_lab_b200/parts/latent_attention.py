@@ -123,7 +123,8 @@ class LatentAttention(Mixer):
         n, heads, width = queries.shape[0], self.n_heads, self.key_width
         if queries.dtype == torch.bfloat16 and self.value_width == width:
             attended = ctx.empty((n, heads * width))
-            attention_mma.attend(ctx, queries, cache, attended, heads, 1, width, self.window, self.scale, shared_rows=True)
+            attention_mma.attend(ctx, queries, cache, attended, heads, 1, width, self.window, self.scale, shared_rows=True,
+                                 value_cols=self.latent_dim)
         else:
             attended = ctx.empty((n, heads * self.latent_dim))
             ops.attention_generic(queries, cache.pages, attended, ctx.positions, ctx.token_row, cache.block_table, heads, 1,
