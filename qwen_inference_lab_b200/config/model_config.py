@@ -421,3 +421,109 @@ class LarolornConfig:
 
     def __eq__(self, other):
         return isinstance(other, LarolornConfig) and self.to_dict() == other.to_dict()
+
+
+class GogotarConfig:
+    """Gogotar: a decoder whose layers are listed one by one in config.json, a run of them looped.
+
+    ``vocab``, ``width``, ``norm.eps``, ``embedding.scale`` (what a token's row is multiplied by), ``logit_softcap``
+    (logits <- cap * tanh(logits / cap)), ``layers`` and ``loop`` (``start``, ``stop``, ``times``: layers
+    start .. stop - 1 run ``times`` times in a row with the same tensors, every pass with a cache of its own).
+    A layer is an ``attention`` mixer (``heads``, ``kv_heads``, ``dim``, ``vdim`` = ``dim`` since the values are the
+    keys, ``scale``, ``softcap``, ``rot`` with ``base``, ``dims`` and optionally ``scaling`` with ``factor``, ``low``,
+    ``high``, ``original``; ``mask.size`` the chunk) or a ``latent_attention`` one (``heads``, ``dim``, ``vdim``,
+    ``kv_rank``, ``q_rank``, ``scale``), and a feed-forward: ``mlp`` null, ``dense`` (``ff``, ``limit``) or ``moe``
+    (``expert.ff``, ``router.experts``, ``router.top``).  The configuration is kept as the dictionary it came in;
+    this class checks it and answers the few questions the engine asks.  ``max_positions`` (not a key of the design;
+    2**20 unless given) only bounds a request.
+    """
+    architecture = "Gogotar"
+    model_type = "gogotar"
+
+    def __init__(self, data: dict):
+        self.data = data
+        for key in ("vocab", "width"):
+            if not _positive_int(data.get(key)):
+                raise ConfigError(f"{key} must be a positive integer, got {data.get(key)!r}")
+        eps = (data.get("norm") or {}).get("eps")
+        if not _positive_number(eps):
+            raise ConfigError(f"norm.eps must be a positive number, got {eps!r}")
+        scale = (data.get("embedding") or {}).get("scale", 1.0)
+        if not _positive_number(scale):
+            raise ConfigError(f"embedding.scale must be a positive number, got {scale!r}")
+        cap = data.get("logit_softcap")
+        if cap is not None and not _positive_number(cap):
+            raise ConfigError(f"logit_softcap must be a positive number or absent, got {cap!r}")
+        layers = data.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError("layers must be a non-empty list")
+        for index, layer in enumerate(layers):
+            where = f"layers[{index}]"
+            kind, mixer = layer.get("type"), layer.get("mixer")
+            if not isinstance(mixer, dict):
+                raise ConfigError(f"{where}.mixer must be an object")
+            if kind == "attention":
+                LarolornConfig._check_sizes(where, mixer, ("heads", "kv_heads", "dim"))
+                if mixer["heads"] % mixer["kv_heads"]:
+                    raise ConfigError(f"{where}: {mixer['heads']} heads do not divide into {mixer['kv_heads']} kv heads")
+                if mixer.get("vdim", mixer["dim"]) != mixer["dim"]:
+                    raise ConfigError(f"{where}: the values are the keys, so vdim must be dim ({mixer['dim']})")
+                LarolornConfig._check_rotation(where, mixer, mixer["dim"])
+                scaling = mixer["rot"].get("scaling")
+                if scaling is not None and (not all(_positive_number(scaling.get(k)) for k in ("factor", "low", "high", "original"))
+                                            or scaling["low"] >= scaling["high"]):
+                    raise ConfigError(f"{where}.rot.scaling needs positive factor, low < high and original; got {scaling!r}")
+                if mixer.get("mask") is not None:
+                    LarolornConfig._check_mask(where, mixer)
+                if mixer.get("softcap") is not None and not _positive_number(mixer["softcap"]):
+                    raise ConfigError(f"{where}.softcap must be a positive number or absent")
+            elif kind == "latent_attention":
+                LarolornConfig._check_sizes(where, mixer, ("heads", "dim", "vdim", "kv_rank", "q_rank"))
+            else:
+                raise ConfigError(f"{where}.type {kind!r} is neither attention nor latent_attention")
+            if not _positive_number(mixer.get("scale")):
+                raise ConfigError(f"{where}: scale must be a positive number, got {mixer.get('scale')!r}")
+            mlp = layer.get("mlp")
+            if mlp is None:
+                continue
+            if mlp.get("kind") == "dense":
+                if not _positive_int(mlp.get("ff")) or not _positive_number(mlp.get("limit")):
+                    raise ConfigError(f"{where}.mlp needs a positive ff and limit")
+            elif mlp.get("kind") == "moe":
+                router, expert = mlp.get("router") or {}, mlp.get("expert") or {}
+                if not _positive_int(expert.get("ff")) or not _positive_int(router.get("experts")) \
+                        or not _positive_int(router.get("top")) or router["top"] > router["experts"]:
+                    raise ConfigError(f"{where}.mlp needs expert.ff, router.experts and router.top <= experts")
+            else:
+                raise ConfigError(f"{where}.mlp.kind {mlp.get('kind')!r} is neither dense nor moe")
+        loop = data.get("loop")
+        if loop is not None:
+            if not all(type(loop.get(k)) is int for k in ("start", "stop", "times")) \
+                    or not 0 <= loop["start"] <= loop["stop"] <= len(layers) or loop["times"] < 1:
+                raise ConfigError(f"loop needs 0 <= start <= stop <= {len(layers)} and times >= 1, got {loop!r}")
+        self.vocab_size, self.width, self.eps = data["vocab"], data["width"], float(eps)
+        self.embedding_scale, self.logit_softcap = float(scale), float(cap or 0.0)
+        self.layers = layers
+        self.max_positions = int(data.get("max_positions", 1 << 20))
+        eos = data.get("eos_token_id")
+        self.eos_token_ids = frozenset() if eos is None else frozenset(eos if isinstance(eos, list) else [eos])
+
+    def layer_runs(self) -> list:
+        """The layers' indices in the order they run."""
+        count, loop = len(self.layers), self.data.get("loop")
+        if loop is None:
+            return list(range(count))
+        return list(range(loop["start"])) + list(range(loop["start"], loop["stop"])) * loop["times"] \
+            + list(range(loop["stop"], count))
+
+    @classmethod
+    def from_dict(cls, data: dict) -> "GogotarConfig":
+        if data.get("architecture", cls.architecture) != cls.architecture:
+            raise ConfigError(f"architecture {data.get('architecture')!r} is not {cls.architecture}")
+        return cls(json.loads(json.dumps(data)))
+
+    def to_dict(self) -> dict:
+        return json.loads(json.dumps(self.data)) | {"architecture": self.architecture}
+
+    def __eq__(self, other):
+        return isinstance(other, GogotarConfig) and self.to_dict() == other.to_dict()

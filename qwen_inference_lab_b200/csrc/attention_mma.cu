@@ -1011,6 +1011,17 @@ extern "C" int qil_attn_prefill_shared(const void* q, const void* kv, void* out,
                           num_pages, window, scale, nullptr, 0.f, nullptr, 0, 0, 0, stream, nullptr, 1, value_cols);
 }
 
+// Shared rows with the options of the MOD kernels (no window then): a softcap, chunks, a sink.
+extern "C" int qil_attn_prefill_shared_modified(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                                const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                                                int page_size, int num_pages, float scale, int value_cols, float softcap,
+                                                const float* dist_bias, int dist_len, int chunk, int sink,
+                                                const float* sink_log2, cudaStream_t stream) {
+    return launch_prefill(q, kv, out, tile_info, n_tiles, block_table, table_stride, n_q_heads, n_kv_heads, page_size,
+                          num_pages, 0, scale, nullptr, softcap, dist_bias, dist_len, chunk, sink, stream, sink_log2, 1,
+                          value_cols);
+}
+
 extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
                                 const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                                 int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
@@ -1088,6 +1099,19 @@ extern "C" int qil_attn_decode_shared(const void* q, const void* kv, void* out, 
     return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, tickets, n_spans, span_len, block_table,
                          table_stride, n_q_heads, n_kv_heads, page_size, num_pages, window, scale, none, stream,
                          nullptr, 0.f, nullptr, 0, 0, 0, nullptr, 1, value_cols);
+}
+
+// Shared rows with the options of the MOD kernels (no window then).
+extern "C" int qil_attn_decode_shared_modified(const void* q, const void* kv, void* out, const int* decode_info,
+                                               int n_decode, float* part_o, float* part_ml, unsigned* tickets, int n_spans,
+                                               int span_len, const int* block_table, int table_stride, int n_q_heads,
+                                               int n_kv_heads, int page_size, int num_pages, float scale, int value_cols,
+                                               float softcap, const float* dist_bias, int dist_len, int chunk, int sink,
+                                               const float* sink_log2, cudaStream_t stream) {
+    DecodeTail none = {};
+    return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, tickets, n_spans, span_len, block_table,
+                         table_stride, n_q_heads, n_kv_heads, page_size, num_pages, 0, scale, none, stream, nullptr,
+                         softcap, dist_bias, dist_len, chunk, sink, sink_log2, 1, value_cols);
 }
 
 // The same with a distance bias per query head (slopes_log2: float32 [n_q_heads], see AttnParams).

@@ -12,14 +12,14 @@ QIL_ERROR_STORAGE
 // ---------------------------------------------------------------- embedding
 template <typename T, typename W>
 __global__ void embed_gather_kernel(const W* __restrict__ table, const int* __restrict__ ids,
-                                    T* __restrict__ out, int width, int vocab) {
+                                    T* __restrict__ out, int width, int vocab, float scale) {
     const int row = blockIdx.x;
     int id = ids[row];
     // Host code validates ids; clamp so that a bad id can never read out of bounds.
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     const W* src = table + (size_t)id * width;
     T* dst = out + (size_t)row * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<T>(to_f32<W>(src[i]));
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<T>(to_f32<W>(src[i]) * scale);
 }
 
 // bfloat16 table and output with a width that allows 16-byte copies
@@ -36,17 +36,18 @@ __global__ void embed_gather_bf16x8_kernel(const bf16* __restrict__ table, const
 }
 
 extern "C" int qil_embed_gather(const void* table, int table_dtype, const int* ids, void* out,
-                                int out_dtype, int n_rows, int width, int vocab, cudaStream_t stream) {
+                                int out_dtype, int n_rows, int width, int vocab, float scale, cudaStream_t stream) {
+    // scale: what every row is multiplied by on its way out (float32 product, one rounding)
     if (n_rows <= 0) return 0;
     if (width <= 0 || vocab <= 0) QIL_REFUSE("embed_gather: width %d vocab %d", width, vocab);
-    if (out_dtype == QIL_BF16 && table_dtype == QIL_BF16 && width % 8 == 0 &&
+    if (scale == 1.0f && out_dtype == QIL_BF16 && table_dtype == QIL_BF16 && width % 8 == 0 &&
         (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
         qil_launch_chained(embed_gather_bf16x8_kernel, dim3(n_rows), dim3(128), 0, stream,
                            (const bf16*)table, ids, (bf16*)out, width, vocab);
         QIL_CHECK_LAUNCH();
     }
     QIL_DISPATCH_2(out_dtype, table_dtype,
-        embed_gather_kernel<T, W><<<n_rows, 256, 0, stream>>>((const W*)table, ids, (T*)out, width, vocab));
+        embed_gather_kernel<T, W><<<n_rows, 256, 0, stream>>>((const W*)table, ids, (T*)out, width, vocab, scale));
     QIL_CHECK_LAUNCH();
 }
 
@@ -384,6 +385,21 @@ __global__ void scale_inplace_kernel(float* __restrict__ x, size_t total, float 
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < total; i += stride) x[i] *= s;
+}
+
+// x <- cap * tanh(x / cap) (float32 rows, e.g. logits)
+__global__ void softcap_inplace_kernel(float* __restrict__ x, size_t total, float cap) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) x[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int qil_softcap_inplace(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (!(cap > 0.f)) QIL_REFUSE("softcap_inplace: a cap of %g", (double)cap);
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    softcap_inplace_kernel<<<blocks, 256, 0, stream>>>(x, (size_t)total, cap);
+    QIL_CHECK_LAUNCH();
 }
 
 extern "C" int qil_scale_inplace(float* x, long long total, float s, cudaStream_t stream) {

@@ -21,6 +21,7 @@
 // Other designs of routing and experts, as options of the same kernels:
 //   route, mode 1   scores = softmax over all outputs of the router; the choice goes by score + correction[e],
 //                   the weights are the chosen scores alone, divided by their sum (+ 1e-20), times weight_scale.
+//   route, mode 2   as mode 1, but the chosen scores are the weights as they are (times weight_scale): no division.
 //                   One more row behind the router's (`gate_logit`) is a dot product that is handed out as it is:
 //                   the logit of a gate, one number per token, for an expert that every token uses.
 //   experts         without a gate matrix: h = act(A W_up[e]^T) with act the squared relu (kind 3), silu or gelu.
@@ -59,7 +60,7 @@ __device__ __forceinline__ void moe_select(float* logits, float* choice, float* 
     if (gate_logit != nullptr) {
         if (lane == 0) gate_logit[token] = logits[n_outputs];
     }
-    if (mode == 1) {
+    if (mode >= 1) {
         // softmax over all outputs; the choice by score + correction, the weights from the scores alone
         float peak = -INFINITY;
         for (int e = lane; e < n_outputs; e += 32) peak = fmaxf(peak, logits[e]);
@@ -98,7 +99,8 @@ __device__ __forceinline__ void moe_select(float* logits, float* choice, float* 
         }
         for (int k = lane; k < top; k += 32) {
             chosen[token * top + k] = sel_at[k];
-            weights[token * top + k] = sel_p[k] / (picked + 1e-20f) * weight_scale;
+            // mode 2: the chosen scores weigh their experts as they are, not divided by their sum
+            weights[token * top + k] = (mode == 2 ? sel_p[k] : sel_p[k] / (picked + 1e-20f)) * weight_scale;
         }
         return;
     }
@@ -697,7 +699,7 @@ extern "C" int qil_moe_route(const void* x, const void* router, const void* bias
     if (n_experts <= 0 || n_experts + (gate_logit != nullptr ? 1 : 0) > MOE_MAX_EXPERTS || top <= 0 || top > n_experts
         || top > MOE_MAX_TOP || width <= 0)
         QIL_REFUSE("moe_route: %d experts (at most %d), %d of them per token, width %d", n_experts, MOE_MAX_EXPERTS, top, width);
-    if (mode != 0 && mode != 1) QIL_REFUSE("moe_route: mode %d", mode);
+    if (mode < 0 || mode > 2) QIL_REFUSE("moe_route: mode %d", mode);
     if (gate_logit != nullptr && bias != nullptr) QIL_REFUSE("moe_route: a gate row goes without router biases");
     if (n_tokens >= 64 && width % 8 == 0 && (((uintptr_t)x | (uintptr_t)router) & 15) == 0) {
         QIL_DISPATCH_2(act_dtype, weight_dtype,

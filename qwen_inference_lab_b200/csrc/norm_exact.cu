@@ -13,12 +13,12 @@
 template <typename TI, typename TO, typename W>
 __global__ void __launch_bounds__(256)
 rmsnorm_exact_kernel(const TI* __restrict__ x, const W* __restrict__ weight, const int* __restrict__ rows,
-                     TO* __restrict__ out, int width, float eps, float offset) {
+                     TO* __restrict__ out, int width, float eps, float offset, long long ld) {
     __shared__ float scratch[32];
     qil_wait_for_producer();
     qil_release_consumer();
     const int r = blockIdx.x;
-    const TI* src = x + (size_t)(rows ? rows[r] : r) * width;
+    const TI* src = x + (size_t)(rows ? rows[r] : r) * (size_t)ld;      // ld: the input's row stride (a column range of a wider buffer)
     TO* dst = out + (size_t)r * width;
     float sq = 0.f;
     for (int i = threadIdx.x; i < width; i += 256) {
@@ -33,17 +33,17 @@ rmsnorm_exact_kernel(const TI* __restrict__ x, const W* __restrict__ weight, con
 
 extern "C" int qil_rmsnorm_exact(const void* x, int x_dtype, const void* weight, int weight_dtype, const int* rows,
                                  void* out, int out_dtype, int n_rows, int width, float eps, float offset,
-                                 cudaStream_t stream) {
+                                 long long ld, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (width <= 0) QIL_REFUSE("rmsnorm_exact: width %d", width);
+    if (width <= 0 || ld < width) QIL_REFUSE("rmsnorm_exact: width %d, row stride %lld", width, ld);
 #define QIL_NORM_GO(TI, TO)                                                                                  \
     do {                                                                                                     \
         if (weight_dtype == QIL_F32)                                                                         \
             qil_launch_chained(rmsnorm_exact_kernel<TI, TO, float>, dim3(n_rows), dim3(256), 0, stream,      \
-                               (const TI*)x, (const float*)weight, rows, (TO*)out, width, eps, offset);      \
+                               (const TI*)x, (const float*)weight, rows, (TO*)out, width, eps, offset, ld);  \
         else                                                                                                 \
             qil_launch_chained(rmsnorm_exact_kernel<TI, TO, bf16>, dim3(n_rows), dim3(256), 0, stream,       \
-                               (const TI*)x, (const bf16*)weight, rows, (TO*)out, width, eps, offset);       \
+                               (const TI*)x, (const bf16*)weight, rows, (TO*)out, width, eps, offset, ld);   \
     } while (0)
     if (weight_dtype != QIL_F32 && weight_dtype != QIL_BF16) QIL_REFUSE("rmsnorm_exact: weight dtype %d", weight_dtype);
     if (x_dtype == QIL_F32 && out_dtype == QIL_F32) QIL_NORM_GO(float, float);
@@ -55,7 +55,7 @@ extern "C" int qil_rmsnorm_exact(const void* x, int x_dtype, const void* weight,
     QIL_CHECK_LAUNCH();
 }
 
-// Layer norm with weight and bias, float32 from end to end like the norm above:
+// Layer norm with weight and bias (null: none), float32 from end to end like the norm above:
 //
 //   y = (x - mean) / sqrt(var + eps) * w + b,     var = mean((x - mean)^2)
 //
@@ -81,7 +81,7 @@ layernorm_exact_kernel(const TI* __restrict__ x, const W* __restrict__ weight, c
     sq = block_sum(sq, scratch);
     const float scale = 1.0f / sqrtf(sq / (float)width + eps);
     for (int i = threadIdx.x; i < width; i += 256)
-        dst[i] = from_f32<TO>((to_f32<TI>(src[i]) - mean) * scale * to_f32<W>(weight[i]) + to_f32<W>(bias[i]));
+        dst[i] = from_f32<TO>((to_f32<TI>(src[i]) - mean) * scale * to_f32<W>(weight[i]) + (bias != nullptr ? to_f32<W>(bias[i]) : 0.f));
 }
 
 extern "C" int qil_layernorm_exact(const void* x, int x_dtype, const void* weight, const void* bias, int weight_dtype,
@@ -236,5 +236,81 @@ extern "C" int qil_rms_join(void* x, int x_dtype, const void* a, const void* wa,
 #undef QIL_JOIN_W
 #undef QIL_JOIN_GO
     if (err != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(err)); return (int)err; }
+    QIL_CHECK_LAUNCH();
+}
+
+// A branch joins the stream through a norm on the branch, and the next sublayer's norm of the new stream rides along:
+//   x += norm(a; w),   rows = norm(x; next_w)          (rows and next_w are optional; rows without next_w: x rounded)
+// where norm is the root-mean-square norm (center 0) or the layer norm without a bias (center 1: the mean is taken
+// off first, the variance is the mean of the squared deviations).  float32 arithmetic, every reduction a fixed tree
+// over one row; x is the stream (float32 or bfloat16), a the branch (float32), rows what the next product reads.
+template <typename TX, typename W, typename TO>
+__global__ void __launch_bounds__(256)
+norm_join_kernel(TX* __restrict__ x, const float* __restrict__ a, const W* __restrict__ w, int width, float eps, int center,
+                 const W* __restrict__ next_w, float next_eps, int next_center, TO* __restrict__ rows) {
+    __shared__ float scratch[32];
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const float* ra = a + (size_t)blockIdx.x * width;
+    TX* dst = x + (size_t)blockIdx.x * width;
+    float mean = 0.f;
+    if (center) {
+        float sum = 0.f;
+        for (int i = threadIdx.x; i < width; i += 256) sum += ra[i];
+        mean = block_sum(sum, scratch) / (float)width;
+    }
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < width; i += 256) {
+        const float v = ra[i] - mean;
+        sq = fmaf(v, v, sq);
+    }
+    sq = block_sum(sq, scratch);
+    const float scale = 1.0f / sqrtf(sq / (float)width + eps);
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < width; i += 256) {       // a thread reads back below what it wrote itself
+        const TX next = from_f32<TX>(to_f32<TX>(dst[i]) + (ra[i] - mean) * scale * to_f32<W>(w[i]));
+        dst[i] = next;
+        sum += to_f32<TX>(next);
+    }
+    if (rows == nullptr) return;
+    TO* out = rows + (size_t)blockIdx.x * width;
+    if (next_w == nullptr) {
+        for (int i = threadIdx.x; i < width; i += 256) out[i] = from_f32<TO>(to_f32<TX>(dst[i]));
+        return;
+    }
+    mean = 0.f;
+    if (next_center) mean = block_sum(sum, scratch) / (float)width;
+    sq = 0.f;
+    for (int i = threadIdx.x; i < width; i += 256) {
+        const float v = to_f32<TX>(dst[i]) - mean;
+        sq = fmaf(v, v, sq);
+    }
+    sq = block_sum(sq, scratch);
+    const float next_scale = 1.0f / sqrtf(sq / (float)width + next_eps);
+    for (int i = threadIdx.x; i < width; i += 256)
+        out[i] = from_f32<TO>((to_f32<TX>(dst[i]) - mean) * next_scale * to_f32<W>(next_w[i]));
+}
+
+extern "C" int qil_norm_join(void* x, int x_dtype, const float* a, const void* w, int weight_dtype, int n_rows, int width,
+                             float eps, int center, const void* next_w, float next_eps, int next_center, void* rows,
+                             int rows_dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (width <= 0) QIL_REFUSE("norm_join: width %d", width);
+    if (next_w != nullptr && rows == nullptr) QIL_REFUSE("norm_join: the next norm needs rows to write");
+#define QIL_JOIN_GO(TX, WT, TO)                                                                                     \
+    qil_launch_chained(norm_join_kernel<TX, WT, TO>, dim3(n_rows), dim3(256), 0, stream, (TX*)x, a, (const WT*)w,   \
+                       width, eps, center, (const WT*)next_w, next_eps, next_center, (TO*)rows)
+#define QIL_JOIN_O(TX, WT)                                                                                          \
+    do { if (rows_dtype == QIL_F32) QIL_JOIN_GO(TX, WT, float); else QIL_JOIN_GO(TX, WT, bf16); } while (0)
+#define QIL_JOIN_W(TX)                                                                                              \
+    do { if (weight_dtype == QIL_F32) QIL_JOIN_O(TX, float); else QIL_JOIN_O(TX, bf16); } while (0)
+    if (weight_dtype != QIL_F32 && weight_dtype != QIL_BF16) QIL_REFUSE("norm_join: weight dtype %d", weight_dtype);
+    if (rows != nullptr && rows_dtype != QIL_F32 && rows_dtype != QIL_BF16) QIL_REFUSE("norm_join: rows dtype %d", rows_dtype);
+    if (x_dtype == QIL_F32) QIL_JOIN_W(float);
+    else if (x_dtype == QIL_BF16) QIL_JOIN_W(bf16);
+    else QIL_REFUSE("norm_join: stream dtype %d", x_dtype);
+#undef QIL_JOIN_W
+#undef QIL_JOIN_O
+#undef QIL_JOIN_GO
     QIL_CHECK_LAUNCH();
 }

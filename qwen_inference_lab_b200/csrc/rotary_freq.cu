@@ -9,7 +9,8 @@
 //
 // qk_rotate_store: q [Hq * d], k [Hkv * d], v [Hkv * e] are column ranges of one row-major buffer (a stacked
 // projection).  Optionally q and k are first divided by their root mean square over the WHOLE projection (all
-// heads at once) and multiplied by a weight per element (float32 arithmetic); then every head is rotated;
+// heads at once) and multiplied by a weight per element (float32 arithmetic), or (per_head) every head by its own
+// root mean square over its d dimensions, with one weight of d that all heads share; then every head is rotated;
 // queries go to q_out, keys and values into the request's page (a page holds its key rows
 // [kv_head][slot][d] followed by its value rows [kv_head][slot][e]).
 //
@@ -61,7 +62,7 @@ qk_rotate_store_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col,
                        T* __restrict__ pages, const W* __restrict__ q_norm_w, const W* __restrict__ k_norm_w, float eps,
                        const float* __restrict__ freq, int rot_dims, int layout, const int* __restrict__ positions,
                        const int* __restrict__ token_row, const int* __restrict__ block_table, int table_stride,
-                       int n_q_heads, int n_kv_heads, int d, int e, int page_size, int num_pages, int wide) {
+                       int n_q_heads, int n_kv_heads, int d, int e, int page_size, int num_pages, int wide, int per_head) {
     constexpr int V = 16 / (int)sizeof(T);
     extern __shared__ __align__(16) float vals[];   // [Hq * d + Hkv * d]: q then k, normed, float32;  then [rot_dims]: the angles
     __shared__ float scratch[32];
@@ -89,7 +90,20 @@ qk_rotate_store_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col,
         for (int i = tid; i < q_width; i += 256) { const float x = to_f32<T>(row[q_col + i]); vals[i] = x; sq = fmaf(x, x, sq); }
         for (int i = tid; i < k_width; i += 256) { const float x = to_f32<T>(row[k_col + i]); vals[q_width + i] = x; sk = fmaf(x, x, sk); }
     }
-    if (q_norm_w != nullptr) {
+    if (q_norm_w != nullptr && per_head) {
+        // a warp per head: the head's sum of squares by a fixed tree over the lanes, whatever else the step holds
+        __syncthreads();
+        const int lane = tid & 31, warp = tid >> 5;
+        for (int head = warp; head < n_q_heads + n_kv_heads; head += 8) {
+            float* v = vals + head * d;
+            const W* w = head < n_q_heads ? q_norm_w : k_norm_w;
+            float ss = 0.f;
+            for (int j = lane; j < d; j += 32) ss = fmaf(v[j], v[j], ss);
+            ss = warp_sum(ss);
+            const float r = 1.0f / sqrtf(ss / (float)d + eps);
+            for (int j = lane; j < d; j += 32) v[j] = v[j] * r * to_f32<W>(w[j]);
+        }
+    } else if (q_norm_w != nullptr) {
         sq = block_sum(sq, scratch);
         sk = block_sum(sk, scratch);
         const float rq = 1.0f / sqrtf(sq / (float)q_width + eps);
@@ -146,7 +160,8 @@ extern "C" int qil_qk_rotate_store(const void* proj, int ld, int q_col, int k_co
                                    const void* q_norm_w, const void* k_norm_w, int norm_dtype, float eps, const float* freq,
                                    int rot_dims, int layout, const int* positions, const int* token_row,
                                    const int* block_table, int table_stride, int n_tokens, int n_q_heads, int n_kv_heads,
-                                   int d, int e, int page_size, int num_pages, int act_dtype, cudaStream_t stream) {
+                                   int d, int e, int page_size, int num_pages, int act_dtype, int per_head,
+                                   cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_q_heads <= 0 || n_kv_heads < 0 || d <= 0 || e <= 0 || page_size <= 0)
         QIL_REFUSE("qk_rotate_store: heads %d/%d sizes %d/%d page %d", n_q_heads, n_kv_heads, d, e, page_size);
@@ -167,7 +182,7 @@ extern "C" int qil_qk_rotate_store(const void* proj, int ld, int q_col, int k_co
             qil_launch_chained(qk_rotate_store_kernel<T, W>, dim3(n_tokens), dim3(256), smem, stream,
                                (const T*)proj, ld, q_col, k_col, v_col, (T*)q_out, (T*)pages, (const W*)q_norm_w,
                                (const W*)k_norm_w, eps, freq, rot_dims, layout, positions, token_row, block_table,
-                               table_stride, n_q_heads, n_kv_heads, d, e, page_size, num_pages, wide);
+                               table_stride, n_q_heads, n_kv_heads, d, e, page_size, num_pages, wide, per_head);
     });
     if (err != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(err)); return (int)err; }
     QIL_CHECK_LAUNCH();
@@ -252,7 +267,8 @@ extern "C" int qil_latent_prepare(const void* proj, int ld, int q_col, int kv_co
     QIL_CHECK_LAUNCH();
 }
 
-// Products per head: y[n][h][j] = (sum_i w[h][j][i] * x[n][h][i]) (* sigmoid(gate[n][h])), j < n_out, i < n_in.
+// Products per head: y[n][h][j] = (sum_i w[h][j][i] * x[n][h][i]) (* sigmoid(gate[n][h])), j < n_out, i < n_in
+// (gate_each: a gate per output, gate[n][h * n_out + j], instead of one per head).
 // x, y and gate are given by the address of head 0's first element of token 0, a row stride and a head stride
 // (in elements), so they may be column ranges of wider buffers.  float32 sums in ascending i within a lane's
 // share, then a fixed tree over the lanes: a row's result does not depend on the other rows of the launch.
@@ -261,7 +277,7 @@ template <typename T, typename W>
 __global__ void __launch_bounds__(256)
 head_product_kernel(const T* __restrict__ x, long long x_row, int x_head, const W* __restrict__ w, T* __restrict__ y,
                     long long y_row, int y_head, const T* __restrict__ gate, long long gate_row, int n_tokens,
-                    int n_in, int n_out) {
+                    int n_in, int n_out, int gate_each) {
     extern __shared__ float xs[];             // [HP_TOKENS][n_in]
     qil_wait_for_producer();
     qil_release_consumer();
@@ -291,7 +307,7 @@ head_product_kernel(const T* __restrict__ x, long long x_row, int x_head, const 
 #pragma unroll
             for (int t = 0; t < HP_TOKENS; ++t) if (t == lane) v = acc[t];
             if (gate != nullptr) {
-                const float g = to_f32<T>(gate[(size_t)(t0 + lane) * gate_row + head]);
+                const float g = to_f32<T>(gate[(size_t)(t0 + lane) * gate_row + (gate_each ? head * n_out + j : head)]);
                 v *= 1.f / (1.f + expf(-g));
             }
             y[(size_t)(t0 + lane) * y_row + (size_t)head * y_head + j] = from_f32<T>(v);
@@ -301,7 +317,7 @@ head_product_kernel(const T* __restrict__ x, long long x_row, int x_head, const 
 
 extern "C" int qil_head_product(const void* x, long long x_row, int x_head, const void* w, void* y, long long y_row,
                                 int y_head, const void* gate, long long gate_row, int n_tokens, int n_heads, int n_in,
-                                int n_out, int act_dtype, int weight_dtype, cudaStream_t stream) {
+                                int n_out, int act_dtype, int weight_dtype, int gate_each, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_heads <= 0 || n_heads > 65535 || n_in <= 0 || n_out <= 0)
         QIL_REFUSE("head_product: %d heads of %d -> %d", n_heads, n_in, n_out);
@@ -318,7 +334,7 @@ extern "C" int qil_head_product(const void* x, long long x_row, int x_head, cons
         if (err == cudaSuccess)
             qil_launch_chained(head_product_kernel<T, W>, dim3(tiles, n_heads, split), dim3(256), smem, stream,
                                (const T*)x, x_row, x_head, (const W*)w, (T*)y, y_row, y_head, (const T*)gate, gate_row,
-                               n_tokens, n_in, n_out);
+                               n_tokens, n_in, n_out, gate_each);
     });
     if (err != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(err)); return (int)err; }
     QIL_CHECK_LAUNCH();

@@ -231,13 +231,22 @@ def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_head
     """tile_info int32 [n_tiles * 4]: (first token, its position, rows <= 64, block-table row) per tile.
     ``slopes_log2`` float32 [Hq]: slope_h * log2(e) of a bias slope_h * (query position - key position) that is
     taken off the scaled score.  ``options``: a :class:`ScoreOptions` (no window then).  ``shared_rows``: a page
-    holds one row per position, the key, whose leading ``value_cols`` columns (0: all) are the value (no slopes or
-    options then); the output's columns past those are zero."""
+    holds one row per position, the key, whose leading ``value_cols`` columns (0: all) are the value (no slopes
+    then; options go with it); the output's columns past those are zero."""
     lib = library(head_dim)
     _check_slopes(slopes_log2, n_q_heads)
+    if shared_rows and options:
+        options.check(n_q_heads)
+        if window or slopes_log2 is not None:
+            raise KernelError("attention: score options over shared rows go without a window and slopes")
+        _check(lib, lib.qil_attn_prefill_shared_modified(
+            _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), _p(block_table), c_int(block_table.shape[1]),
+            c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_float(scale),
+            c_int(int(value_cols)), *options.arguments(), _stream()), "attention (prompt portions)")
+        return
     if shared_rows:
-        if options or slopes_log2 is not None:
-            raise KernelError("attention: shared rows go without slopes and score options")
+        if slopes_log2 is not None:
+            raise KernelError("attention: shared rows go without slopes")
         _check(lib, lib.qil_attn_prefill_shared(
             _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), _p(block_table), c_int(block_table.shape[1]),
             c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_int(window),
@@ -268,9 +277,19 @@ def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_
     second kernel does.  ``shared_rows``: see ``prefill``."""
     lib = library(head_dim)
     _check_slopes(slopes_log2, n_q_heads)
+    if shared_rows and options:
+        options.check(n_q_heads)
+        if window or slopes_log2 is not None:
+            raise KernelError("attention: score options over shared rows go without a window and slopes")
+        _check(lib, lib.qil_attn_decode_shared_modified(
+            _p(q), _p(pages), _p(out), _p(decode_info), c_int(n_decode), _p(part_o), _p(part_ml), _p(tickets), c_int(n_spans),
+            c_int(span_len), _p(block_table), c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads),
+            c_int(page_size), c_int(pages.shape[0]), c_float(scale), c_int(int(value_cols)), *options.arguments(),
+            _stream()), "attention (single tokens)", kernels=1 if tickets is not None else 2)
+        return
     if shared_rows:
-        if options or slopes_log2 is not None:
-            raise KernelError("attention: shared rows go without slopes and score options")
+        if slopes_log2 is not None:
+            raise KernelError("attention: shared rows go without slopes")
         _check(lib, lib.qil_attn_decode_shared(
             _p(q), _p(pages), _p(out), _p(decode_info), c_int(n_decode), _p(part_o), _p(part_ml), _p(tickets), c_int(n_spans),
             c_int(span_len), _p(block_table), c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads),

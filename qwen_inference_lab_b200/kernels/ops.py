@@ -139,15 +139,16 @@ def _need(tensor, name, dtype=None, ndim=None):
         raise KernelError(f"{name} must have {ndim} dimensions, got {tuple(tensor.shape)}")
 
 
-def embed_gather(table, ids, out):
-    """out[r] = table[ids[r]] cast to out's dtype.  table [V,H]; ids int32 [N]; out [N,H]."""
+def embed_gather(table, ids, out, scale=1.0):
+    """out[r] = table[ids[r]] * scale cast to out's dtype (a float32 product, one rounding).  table [V,H]; ids int32
+    [N]; out [N,H]."""
     _need(table, "table", ndim=2); _need(ids, "ids", torch.int32, 1); _need(out, "out", ndim=2)
     if out.shape != (ids.shape[0], table.shape[1]):
         raise KernelError(f"embed_gather: out {tuple(out.shape)} for ids {tuple(ids.shape)} table {tuple(table.shape)}")
     lib = core()
     _check(lib, lib.qil_embed_gather(_p(table), c_int(dtype_code(table.dtype)), _p(ids), _p(out),
                                      c_int(dtype_code(out.dtype)), c_int(ids.shape[0]), c_int(table.shape[1]),
-                                     c_int(table.shape[0]), _stream()), "embed_gather")
+                                     c_int(table.shape[0]), c_float(scale), _stream()), "embed_gather")
     return out
 
 
@@ -439,11 +440,15 @@ def attention_generic(q, kv_cache, out, positions, token_row, block_table, n_q_h
     return out
 
 
-def rmsnorm_exact(x, weight, eps, offset=0.0, out_dtype=None, rows=None, out=None):
+def rmsnorm_exact(x, weight, eps, offset=0.0, out_dtype=None, rows=None, out=None, columns=None):
     """y = x / sqrt(mean(x^2) + eps) * (offset + weight) with float32 arithmetic and one rounding.
-    ``x`` float32 or bfloat16 [N, width]; the result has ``out_dtype`` (default: x's)."""
+    ``x`` float32 or bfloat16 [N, width]; the result has ``out_dtype`` (default: x's).  ``columns`` = (first, width):
+    the norm is over that column range of ``x`` alone (a piece of a stacked projection)."""
     _need(x, "x", ndim=2); _need(weight, "weight", ndim=1)
-    width = x.shape[1]
+    ld = x.shape[1]
+    first, width = (0, ld) if columns is None else (int(columns[0]), int(columns[1]))
+    if first < 0 or width <= 0 or first + width > ld:
+        raise KernelError(f"rmsnorm_exact: columns {first} .. {first + width} of {ld}")
     if weight.shape[0] != width:
         raise KernelError(f"rmsnorm_exact: weight of {weight.shape[0]} for width {width}")
     if rows is not None:
@@ -455,19 +460,23 @@ def rmsnorm_exact(x, weight, eps, offset=0.0, out_dtype=None, rows=None, out=Non
     if out.shape != (n_rows, width):
         raise KernelError("rmsnorm_exact: out has the wrong shape")
     lib = core()
-    _check(lib, lib.qil_rmsnorm_exact(_p(x), c_int(dtype_code(x.dtype)), _p(weight), c_int(dtype_code(weight.dtype)),
+    _check(lib, lib.qil_rmsnorm_exact(c_void_p(x.data_ptr() + first * x.element_size()), c_int(dtype_code(x.dtype)),
+                                      _p(weight), c_int(dtype_code(weight.dtype)),
                                       _p(rows), _p(out), c_int(dtype_code(out.dtype)), c_int(n_rows), c_int(width),
-                                      c_float(eps), c_float(offset), _stream()), "rmsnorm_exact")
+                                      c_float(eps), c_float(offset), c_longlong(ld), _stream()), "rmsnorm_exact")
     return out
 
 
 def layernorm_exact(x, weight, bias, eps, out_dtype=None, rows=None, out=None):
     """y = (x - mean) / sqrt(var + eps) * weight + bias with float32 arithmetic and one rounding; var is the mean
-    of the squared deviations.  ``x`` float32 or bfloat16 [N, width]; the result has ``out_dtype`` (default: x's)."""
-    _need(x, "x", ndim=2); _need(weight, "weight", ndim=1); _need(bias, "bias", weight.dtype, 1)
+    of the squared deviations.  ``x`` float32 or bfloat16 [N, width]; the result has ``out_dtype`` (default: x's).
+    ``bias`` None: a layer norm without one."""
+    _need(x, "x", ndim=2); _need(weight, "weight", ndim=1)
     width = x.shape[1]
-    if weight.shape[0] != width or bias.shape[0] != width:
-        raise KernelError(f"layernorm_exact: weight of {weight.shape[0]}, bias of {bias.shape[0]} for width {width}")
+    if bias is not None:
+        _need(bias, "bias", weight.dtype, 1)
+    if weight.shape[0] != width or (bias is not None and bias.shape[0] != width):
+        raise KernelError(f"layernorm_exact: weight of {weight.shape[0]} (or the bias) for width {width}")
     if rows is not None:
         _need(rows, "rows", torch.int32, 1)
     n_rows = x.shape[0] if rows is None else rows.shape[0]
@@ -777,6 +786,45 @@ def rms_join(x, a, weight, eps, mult=1.0, *, b=None, weight_a=None, weight_b=Non
     return x
 
 
+def softcap_inplace(x, cap):
+    """x <- cap * tanh(x / cap) for float32 ``x`` (logits)."""
+    _need(x, "x", torch.float32)
+    lib = core()
+    _check(lib, lib.qil_softcap_inplace(_p(x), c_longlong(x.numel()), c_float(cap), _stream()), "softcap_inplace")
+    return x
+
+
+NORM_KINDS = {"rms": 0, "layer": 1}     # root mean square; mean taken off first (a layer norm without a bias)
+
+
+def norm_join(x, branch, weight, eps, kind="rms", *, next_weight=None, next_eps=None, next_kind=None, rows=None):
+    """x += norm(branch) * weight row by row in float32 (``kind``: ``"rms"`` or ``"layer"``, the layer norm without a
+    bias): a float32 branch joins the stream ``x`` (float32 or bfloat16 [N, width], updated in place) through a norm
+    on the branch.  ``rows`` [N, width] (bfloat16 or float32) receives what the next sublayer reads: with
+    ``next_weight`` the norm of the new stream (``next_kind``, ``next_eps``; the defaults are this norm's), without it
+    the new stream rounded."""
+    _need(x, "x", ndim=2); _need(branch, "branch", torch.float32, 2); _need(weight, "weight", ndim=1)
+    if branch.shape != x.shape or weight.shape[0] != x.shape[1]:
+        raise KernelError("norm_join: shapes differ")
+    if kind not in NORM_KINDS or (next_kind or kind) not in NORM_KINDS:
+        raise KernelError(f"norm_join: a norm is one of {sorted(NORM_KINDS)}")
+    if rows is not None:
+        _need(rows, "rows", ndim=2)
+        if rows.shape != x.shape:
+            raise KernelError("norm_join: the next sublayer's rows have another shape")
+    if next_weight is not None:
+        _need(next_weight, "next_weight", weight.dtype, 1)
+        if rows is None or next_weight.shape != weight.shape:
+            raise KernelError("norm_join: the next norm needs rows to write and a weight of the same size")
+    lib = core()
+    _check(lib, lib.qil_norm_join(_p(x), c_int(dtype_code(x.dtype)), _p(branch), _p(weight), c_int(dtype_code(weight.dtype)),
+                                  c_int(x.shape[0]), c_int(x.shape[1]), c_float(eps), c_int(NORM_KINDS[kind]),
+                                  _p(next_weight), c_float(eps if next_eps is None else next_eps),
+                                  c_int(NORM_KINDS[next_kind or kind]), _p(rows),
+                                  c_int(dtype_code(rows.dtype) if rows is not None else 0), _stream()), "norm_join")
+    return x
+
+
 def scale_inplace(x, factor):
     """x *= factor for float32 ``x`` (logits)."""
     _need(x, "x", torch.float32)
@@ -798,12 +846,15 @@ def _check_rotation(freq, rot_dims, layout, most, what):
 
 
 def qk_rotate_store(proj, columns, q_out, kv_cache, q_norm_w, k_norm_w, eps, freq, rot_dims, layout, positions,
-                    token_row, block_table, n_q_heads, n_kv_heads, head_dim, v_dim, page_size):
+                    token_row, block_table, n_q_heads, n_kv_heads, head_dim, v_dim, page_size, per_head=False):
     """The tail of a q/k/v projection with rotation from frequencies (float32 angles position * freq[i]).
 
     ``proj`` [N, width] holds q, k, v from the columns ``columns`` = (q, k, v) on.  With ``q_norm_w`` [Hq * d] and
     ``k_norm_w`` [Hkv * d], q and k are first divided by their root mean square over the whole projection (all heads
-    at once) and multiplied by the weight.  Then the first ``rot_dims`` dimensions of every head are rotated
+    at once) and multiplied by the weight; with ``per_head`` every head is normed by itself over its d dimensions and
+    the weights are [d], one for all query heads and one for all key heads.  The values are copied as projected from
+    column v on: giving the keys' column there stores the keys as projected, before norm and rotation, as values.
+    Then the first ``rot_dims`` dimensions of every head are rotated
     (``layout``: ``ROTARY_HALVES`` or ``ROTARY_INTERLEAVED``); queries go to ``q_out`` [N, Hq * d], keys and values
     into the pages."""
     _need(proj, "proj", ndim=2); _need(q_out, "q_out", proj.dtype, 2)
@@ -818,7 +869,10 @@ def qk_rotate_store(proj, columns, q_out, kv_cache, q_norm_w, k_norm_w, eps, fre
         _need(q_norm_w, "q_norm_w", ndim=1)
         if n_kv_heads:
             _need(k_norm_w, "k_norm_w", q_norm_w.dtype, 1)
-        if q_norm_w.shape[0] != n_q_heads * head_dim or (n_kv_heads and k_norm_w.shape[0] != n_kv_heads * head_dim):
+        if per_head:
+            if q_norm_w.shape[0] != head_dim or (n_kv_heads and k_norm_w.shape[0] != head_dim):
+                raise KernelError("qk_rotate_store: a per-head norm has one weight per dimension of a head")
+        elif q_norm_w.shape[0] != n_q_heads * head_dim or (n_kv_heads and k_norm_w.shape[0] != n_kv_heads * head_dim):
             raise KernelError("qk_rotate_store: the norm weights cover the whole projections")
         norm_code = dtype_code(q_norm_w.dtype)
     _need(positions, "positions", torch.int32, 1); _need(token_row, "token_row", torch.int32, 1)
@@ -833,8 +887,8 @@ def qk_rotate_store(proj, columns, q_out, kv_cache, q_norm_w, k_norm_w, eps, fre
         _p(q_norm_w), _p(k_norm_w), c_int(norm_code), c_float(eps), _p(freq), c_int(rot_dims), c_int(layout),
         _p(positions), _p(token_row), _p(block_table if n_kv_heads else None),
         c_int(block_table.shape[1] if n_kv_heads else 0), c_int(n), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim),
-        c_int(v_dim), c_int(page_size), c_int(num_pages), c_int(dtype_code(proj.dtype)), _stream()),
-        "qk_rotate_store")
+        c_int(v_dim), c_int(page_size), c_int(num_pages), c_int(dtype_code(proj.dtype)), c_int(1 if per_head else 0),
+        _stream()), "qk_rotate_store")
     return q_out
 
 
@@ -849,8 +903,8 @@ def latent_prepare(proj, q_column, kv_column, q_att, kv_cache, norm_w, eps, freq
     _need(proj, "proj", ndim=2); _need(q_att, "q_att", proj.dtype, 2); _need(norm_w, "norm_w", ndim=1)
     n, ld = proj.shape
     width = latent_dim + rot_dim
-    if q_att.shape != (n, n_heads * width) or norm_w.shape[0] != latent_dim \
-            or max(q_column + n_heads * (plain_dim + rot_dim), kv_column + width) > ld:
+    if q_att.shape != (n, n_heads * width) or norm_w.shape[0] != latent_dim or kv_column + width > ld \
+            or (rot_dim > 0 and q_column + n_heads * (plain_dim + rot_dim) > ld):      # without a rotated part q is not read
         raise KernelError("latent_prepare: shapes do not fit together")
     _check_rotation(freq, rot_dims, layout, rot_dim, "latent_prepare")
     _need(positions, "positions", torch.int32, 1); _need(token_row, "token_row", torch.int32, 1)
@@ -866,10 +920,12 @@ def latent_prepare(proj, q_column, kv_column, q_att, kv_cache, norm_w, eps, freq
     return q_att
 
 
-def head_product(x, x_column, x_head_stride, weight, y, y_column, y_head_stride, *, gate=None, gate_column=0):
+def head_product(x, x_column, x_head_stride, weight, y, y_column, y_head_stride, *, gate=None, gate_column=0,
+                 gate_each=False):
     """y[n, y_column + h * y_head_stride + j] = sum_i weight[h, j, i] * x[n, x_column + h * x_head_stride + i], times
     sigmoid(gate[n, gate_column + h]) when ``gate`` is given: one small product per head over column ranges of the
-    row-major buffers ``x`` and ``y`` (float32 sums).  ``weight`` [H, out, in]."""
+    row-major buffers ``x`` and ``y`` (float32 sums).  ``weight`` [H, out, in].  ``gate_each``: a gate per output,
+    sigmoid(gate[n, gate_column + h * out + j]), instead of one per head."""
     _need(x, "x", ndim=2); _need(y, "y", x.dtype, 2); _need(weight, "weight", ndim=3)
     heads, n_out, n_in = weight.shape
     n = x.shape[0]
@@ -879,7 +935,7 @@ def head_product(x, x_column, x_head_stride, weight, y, y_column, y_head_stride,
     gate_ptr, gate_row = c_void_p(0), 0
     if gate is not None:
         _need(gate, "gate", x.dtype, 2)
-        if gate.shape[0] != n or gate_column + heads > gate.shape[1]:
+        if gate.shape[0] != n or gate_column + heads * (n_out if gate_each else 1) > gate.shape[1]:
             raise KernelError("head_product: the gate's columns lie outside its buffer")
         gate_ptr, gate_row = c_void_p(gate.data_ptr() + gate_column * gate.element_size()), gate.shape[1]
     size = x.element_size()
@@ -888,7 +944,7 @@ def head_product(x, x_column, x_head_stride, weight, y, y_column, y_head_stride,
         c_void_p(x.data_ptr() + x_column * size), c_longlong(x.shape[1]), c_int(x_head_stride), _p(weight),
         c_void_p(y.data_ptr() + y_column * size), c_longlong(y.shape[1]), c_int(y_head_stride), gate_ptr,
         c_longlong(gate_row), c_int(n), c_int(heads), c_int(n_in), c_int(n_out), c_int(dtype_code(x.dtype)),
-        c_int(dtype_code(weight.dtype)), _stream()), "head_product")
+        c_int(dtype_code(weight.dtype)), c_int(1 if gate_each else 0), _stream()), "head_product")
     return y
 
 
@@ -906,12 +962,14 @@ def head_gate(y, width, gate, gate_column):
     return y
 
 
-def moe_route(x, router, bias, top, *, softmax_all=False, correction=None, weight_scale=1.0, gate_row=False):
+def moe_route(x, router, bias, top, *, softmax_all=False, correction=None, weight_scale=1.0, gate_row=False,
+              renormalize=True):
     """(chosen int32 [N, top], weights float32 [N, top]): the ``top`` largest of x R^T + b per row (float32
     arithmetic; the lower index wins a tie) and the softmax over those logits alone.
 
     ``softmax_all``: scores are the softmax over all outputs; the choice goes by score + ``correction`` (float32
-    [outputs]), the weights are the chosen scores divided by their sum (+ 1e-20), times ``weight_scale``.
+    [outputs]), the weights are the chosen scores divided by their sum (+ 1e-20), times ``weight_scale``; with
+    ``renormalize=False`` the chosen scores themselves, undivided.
     ``gate_row``: the last row of ``router`` is not an output but a gate's weights: its dot products are returned
     as a third result, float32 [N]."""
     _need(x, "x", ndim=2); _need(router, "router", ndim=2)
@@ -921,6 +979,8 @@ def moe_route(x, router, bias, top, *, softmax_all=False, correction=None, weigh
         _need(bias, "bias", router.dtype, 1)
     n = x.shape[0]
     outputs = router.shape[0] - (1 if gate_row else 0)
+    if not renormalize and not softmax_all:
+        raise KernelError("moe_route: only scores of a softmax over all outputs can stay as they are")
     if correction is not None:
         _need(correction, "correction", torch.float32, 1)
         if correction.shape[0] != outputs:
@@ -930,7 +990,8 @@ def moe_route(x, router, bias, top, *, softmax_all=False, correction=None, weigh
     gate = torch.empty((n,), dtype=torch.float32, device=x.device) if gate_row else None
     lib = core()
     _check(lib, lib.qil_moe_route(_p(x), _p(router), _p(bias), c_int(n), c_int(x.shape[1]), c_int(outputs),
-                                  c_int(top), _p(chosen), _p(weights), c_int(1 if softmax_all else 0), _p(correction),
+                                  c_int(top), _p(chosen), _p(weights), c_int((1 if renormalize else 2) if softmax_all else 0),
+                                  _p(correction),
                                   c_float(weight_scale), _p(gate), c_int(dtype_code(x.dtype)),
                                   c_int(dtype_code(router.dtype)), _stream()), "moe_route")
     return (chosen, weights, gate) if gate_row else (chosen, weights)

@@ -10,6 +10,6 @@ from .experts import RoutedExperts
 from .linear_attention import DecayLinearAttention, GatedLinearAttention
 from .latent_attention import LatentAttention
 from .parallel import ParallelMixers
-from .block import PostNormBlock, PreNormBlock
+from .block import PostNormBlock, PreNormBlock, SandwichNormBlock
 from .side_input import TokenSideInput
 from .decoder import DecoderModel, LayerCall, TokenEmbedding

@@ -29,7 +29,11 @@ A rotation whose angles the kernels compute from frequencies (``position`` a :cl
 layout, on the first dimensions of a head only if so wished) and ``whole_qk_norm_eps`` (q and k are each divided by
 their root mean square over the whole projection, all heads at once, and multiplied by a weight per element
 ``names["q_norm"]``, ``names["k_norm"]``, before the rotation) go with every option above but the per-head norms,
-the short convolution and the query temperature.
+the short convolution and the query temperature.  With such a rotation ``qk_norm_eps`` norms every head by itself
+(one weight of head_dim for all query heads, one for all key heads) in the same kernel.  ``values_from_keys``: there
+is no value projection; a position's value is its key as projected, before norm and rotation.  ``head_gate``: the
+name of a [query heads, hidden] matrix G; head h's output is multiplied by sigmoid(G x)_h before the output
+projection (G's rows ride behind the keys' in the stacked projection).
 """
 from __future__ import annotations
 
@@ -89,7 +93,8 @@ class GroupedQueryAttention(Mixer):
                  qk_norm_eps=None, position=None, window=0, scale=None, reads_shared_cache=False,
                  v_head_dim=None, distance_slopes=None, q_temperature=None, out_bias=None,
                  suffixes=(".weight", ".bias"), conv_taps=0, conv_suffix=".conv", softcap=0.0, distance_bias=None,
-                 chunk=0, sink=False, whole_qk_norm_eps=None, norm_suffix=".weight"):
+                 chunk=0, sink=False, whole_qk_norm_eps=None, norm_suffix=".weight", values_from_keys=False,
+                 head_gate=None):
         if n_q_heads % n_kv_heads:
             raise ValueError(f"{n_q_heads} query heads do not divide into {n_kv_heads} kv heads")
         self.hidden_size, self.head_dim = int(hidden_size), int(head_dim)
@@ -111,10 +116,16 @@ class GroupedQueryAttention(Mixer):
         self.whole_qk_norm_eps = None if whole_qk_norm_eps is None else float(whole_qk_norm_eps)
         # the projection's tail is the kernel that norms over the whole projection and rotates by frequencies
         self.frequency_tail = isinstance(position, RotaryFrequencies) or self.whole_qk_norm_eps is not None
-        if self.frequency_tail and (qk_norm_eps is not None or conv_taps or q_temperature is not None
+        if self.frequency_tail and (conv_taps or q_temperature is not None
+                                    or (qk_norm_eps is not None and self.whole_qk_norm_eps is not None)
                                     or (position is not None and not isinstance(position, RotaryFrequencies))):
-            raise ValueError("rotation from frequencies and the norm over the whole projection go without per-head "
-                             "norms, a rotary table, a short convolution or a query temperature")
+            raise ValueError("rotation from frequencies and the norm over the whole projection go without a rotary "
+                             "table, a short convolution or a query temperature, and with one kind of q/k norm")
+        self.values_from_keys, self.head_gate = bool(values_from_keys), head_gate
+        if (self.values_from_keys or head_gate) and not self.frequency_tail:
+            raise ValueError("keys as values and a gate per head go with the rotation from frequencies")
+        if self.values_from_keys and (reads_shared_cache or (v_head_dim and int(v_head_dim) != int(head_dim))):
+            raise ValueError("keys as values need keys of the layer's own, and values as large as keys")
         if isinstance(position, RotaryFrequencies) and position.rotary_dim > self.head_dim:
             raise ValueError(f"{position.rotary_dim} rotated dimensions in heads of {self.head_dim}")
         if self.conv_taps < 0 or self.softcap < 0 or self.chunk < 0:
@@ -133,7 +144,11 @@ class GroupedQueryAttention(Mixer):
         self._slopes = self._slopes_log2 = None
         pieces = [(names["q"], n_q_heads * head_dim)]
         if not self.reads_shared_cache:
-            pieces += [(names["k"], n_kv_heads * head_dim), (names["v"], n_kv_heads * self.v_head_dim)]
+            pieces += [(names["k"], n_kv_heads * head_dim)]
+            if not self.values_from_keys:
+                pieces += [(names["v"], n_kv_heads * self.v_head_dim)]
+        if head_gate:
+            pieces += [(head_gate, n_q_heads)]
         self.qkv = StackedLinear(hidden_size, pieces, bias=bias, suffixes=suffixes)
         self.out = Linear(n_q_heads * self.v_head_dim, hidden_size, name=names["o"],
                           bias=bias if out_bias is None else out_bias, suffixes=suffixes)
@@ -165,7 +180,7 @@ class GroupedQueryAttention(Mixer):
         if qk_norm_eps is not None:
             self.q_norm = Param((head_dim,), init="norm", std=0.05)
             self.k_norm = Param((head_dim,), init="norm", std=0.05)
-            self._norm_names = (names["q_norm"] + ".weight", names["k_norm"] + ".weight")
+            self._norm_names = (names["q_norm"] + norm_suffix, names["k_norm"] + norm_suffix)
 
     def named_params(self):
         if self._norm_names is None:
@@ -239,15 +254,24 @@ class GroupedQueryAttention(Mixer):
             q = ctx.empty((n, self.n_q_heads * self.head_dim))
             q_width, k_width = self.n_q_heads * self.head_dim, n_kv * self.head_dim
             rotation = self.position
-            ops.qk_rotate_store(qkv, (0, q_width, q_width + k_width), q, cache.pages,
-                                self.whole_q_norm.data if self.whole_q_norm is not None else None,
-                                self.whole_k_norm.data if self.whole_k_norm is not None else None,
-                                self.whole_qk_norm_eps or 0.0, rotation.freq if rotation is not None else None,
+            per_head = self.q_norm is not None
+            q_weight = self.q_norm if per_head else self.whole_q_norm
+            k_weight = self.k_norm if per_head else self.whole_k_norm
+            # keys as values: the value rows are copied from the keys' columns, as projected
+            v_column = q_width if self.values_from_keys else q_width + k_width
+            ops.qk_rotate_store(qkv, (0, q_width, v_column), q, cache.pages,
+                                q_weight.data if q_weight is not None else None,
+                                k_weight.data if k_weight is not None else None,
+                                (self.qk_norm_eps if per_head else self.whole_qk_norm_eps) or 0.0,
+                                rotation.freq if rotation is not None else None,
                                 rotation.rotary_dim if rotation is not None else 0,
                                 rotation.layout if rotation is not None else 0, ctx.positions, ctx.token_row,
-                                cache.block_table, self.n_q_heads, n_kv, self.head_dim, self.v_head_dim, cache.page_size)
+                                cache.block_table, self.n_q_heads, n_kv, self.head_dim, self.v_head_dim, cache.page_size,
+                                per_head=per_head)
             attended = ctx.empty((n, self.n_q_heads * self.v_head_dim))
             self._attend(ctx, q, cache, attended)
+            if self.head_gate:
+                ops.head_gate(attended, self.v_head_dim, qkv, qkv.shape[1] - self.n_q_heads)
             return self.out.forward(ctx, attended, residual=residual, out_scale=out_scale, out_float32=out_float32)
         if out_float32:
             raise ValueError("a float32 result is given by the layers that rotate by frequencies only")

@@ -13,6 +13,7 @@ of the block's.  And parts that run on the stream after the feed-forward (``afte
 
 :class:`PostNormBlock` is the other arrangement: the sublayers read the stream itself and the norm sits on each
 sublayer's output, x <- x + m * norm1(mixer(x)), x <- x + m * norm2(ff(x)) with a fixed multiplier m.
+:class:`SandwichNormBlock` norms on both sides of each sublayer: x <- x + post1(mixer(pre1 x)), x <- x + post2(ff(pre2 x)).
 """
 from __future__ import annotations
 
@@ -142,3 +143,90 @@ class PostNormBlock(Part):
         if copies:
             ctx.extras["stream_rows"] = (x, after)
         return x
+
+
+class SandwichNormBlock(Part):
+    """x <- x + post1(mixer(pre1(x))), then x <- x + post2(ff(pre2(x))): a norm in front of each sublayer and one on its
+    output before it joins the stream, all four of one ``kind`` (``"layer"``: the layer norm without a bias, or
+    ``"rms"``) with a weight each, float32 arithmetic.  The sublayers give float32 rows; ``ops.norm_join`` norms a
+    branch, adds it to the stream and, in the same kernel, norms the new stream for the sublayer that reads it next.
+    That also holds from block to block: a block leaves its feed-forward's branch unjoined in
+    ``ctx.extras["pending_join"]`` and the next block of this kind joins it together with its own first norm; the
+    decoder settles what is left before anyone else reads the stream (:func:`settle_stream`).
+    ``feed_forward`` may be None; the second pair of weights is then optional.
+    names: the four weights' names (pre1, post1, pre2, post2)."""
+    takes_pending_join = True
+
+    def __init__(self, width, eps, mixer, feed_forward, *, names, kind="layer", norm_suffix=".weight"):
+        if kind not in ops.NORM_KINDS:
+            raise ValueError(f"unknown norm {kind!r} (known: {sorted(ops.NORM_KINDS)})")
+        self.width, self.eps, self.kind = int(width), float(eps), kind
+        self.mixer, self.feed_forward = mixer, feed_forward
+        optional = feed_forward is None
+        self.pre1, self.post1 = Param((width,), init="norm", std=0.05), Param((width,), init="norm", std=0.05)
+        self.pre2 = Param((width,), init="norm", std=0.05, optional=optional)
+        self.post2 = Param((width,), init="norm", std=0.05, optional=optional)
+        self._names = {name + norm_suffix: param for name, param in zip(names, (self.pre1, self.post1, self.pre2, self.post2))}
+        if len(names) != 4 or len(self._names) != 4:
+            raise ValueError("a block with norms on both sides of its sublayers has four norm weights")
+        self.graph_safe = True
+
+    def named_params(self):
+        return dict(self._names)
+
+    def children(self):
+        return [part for part in (self.mixer, self.feed_forward) if part is not None]
+
+    def finalize(self, device, dtype):
+        super().finalize(device, dtype)
+        weights = [p for p in (self.pre1, self.post1, self.pre2, self.post2) if p.data is not None]
+        if len({p.data.dtype for p in weights}) > 1:       # one kernel reads two of them: one dtype for all
+            for p in weights:
+                p.data = p.data.float()
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def _normed(self, ctx, x, weight):
+        if self.kind == "layer":
+            return ops.layernorm_exact(x, weight, None, self.eps, out_dtype=ctx.dtype)
+        return ops.rmsnorm_exact(x, weight, self.eps, out_dtype=ctx.dtype)
+
+    def forward(self, ctx, x, cache):
+        """x [N, width] is the residual stream; updated in place and returned."""
+        pending = ctx.extras.pop("pending_join", None)
+        if pending is not None and pending.stream is x and pending.weight.dtype == self.pre1.data.dtype:
+            rows = ctx.empty(x.shape)
+            ops.norm_join(x, pending.branch, pending.weight, pending.eps, pending.kind, next_weight=self.pre1.data,
+                          next_eps=self.eps, next_kind=self.kind, rows=rows)
+        else:
+            if pending is not None:
+                pending.settle()
+            rows = self._normed(ctx, x, self.pre1.data)
+        branch = self.mixer.forward(ctx, rows, cache, out_float32=True)
+        if self.feed_forward is None:
+            ctx.extras["pending_join"] = PendingJoin(x, branch, self.post1.data, self.eps, self.kind)
+            return x
+        rows = ctx.empty(x.shape)
+        ops.norm_join(x, branch, self.post1.data, self.eps, self.kind, next_weight=self.pre2.data, rows=rows)
+        branch = self.feed_forward.forward(ctx, rows, out_float32=True)
+        ctx.extras["pending_join"] = PendingJoin(x, branch, self.post2.data, self.eps, self.kind)
+        return x
+
+
+class PendingJoin:
+    """A normed branch that has not joined its stream yet: stream += norm(branch) * weight."""
+    __slots__ = ("stream", "branch", "weight", "eps", "kind")
+
+    def __init__(self, stream, branch, weight, eps, kind):
+        self.stream, self.branch, self.weight, self.eps, self.kind = stream, branch, weight, eps, kind
+
+    def settle(self):
+        ops.norm_join(self.stream, self.branch, self.weight, self.eps, self.kind)
+
+
+def settle_stream(ctx):
+    """Join what a block left unjoined (see :class:`SandwichNormBlock`); for whoever reads the stream next."""
+    pending = ctx.extras.pop("pending_join", None)
+    if pending is not None:
+        pending.settle()

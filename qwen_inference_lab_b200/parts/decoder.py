@@ -18,6 +18,7 @@ import torch
 
 from ..kernels import ops
 from .base import Param, Part
+from .block import settle_stream
 from .linear import Linear
 
 
@@ -32,8 +33,10 @@ class LayerCall:
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab_size, hidden_size, *, name, suffix=".weight"):
+    def __init__(self, vocab_size, hidden_size, *, name, suffix=".weight", scale=1.0):
+        """``scale``: what a row of the table is multiplied by as it enters the stream."""
         self.vocab_size, self.hidden_size, self.name, self.suffix = int(vocab_size), int(hidden_size), name, suffix
+        self.scale = float(scale)
         self.weight = Param((vocab_size, hidden_size))
 
     def named_params(self):
@@ -43,19 +46,20 @@ class TokenEmbedding(Part):
         """Rows of the table in the dtype of the residual stream (the activations' unless the model keeps
         its stream in float32)."""
         out = ctx.empty((token_ids.shape[0], self.hidden_size), dtype=ctx.stream_dtype)
-        return ops.embed_gather(self.weight.data, token_ids, out)
+        return ops.embed_gather(self.weight.data, token_ids, out, self.scale)
 
 
 class DecoderModel(Part):
     graph_safe = True      # the model itself only walks its parts; they decide
 
     def __init__(self, *, config, embedding, layers, order, final_norm, head, max_positions, stream_dtype=None,
-                 logit_scale=1.0):
+                 logit_scale=1.0, logit_softcap=0.0):
         """``stream_dtype``: the dtype of the residual stream where it is not the activations' (float32 for
         designs that sum their residuals in 32 bits while their products run in bfloat16).
-        ``logit_scale``: what the head's float32 products are multiplied by."""
+        ``logit_scale``: what the head's float32 products are multiplied by.
+        ``logit_softcap`` > 0: logits <- cap * tanh(logits / cap) after that."""
         self.config = config
-        self.logit_scale = float(logit_scale)
+        self.logit_scale, self.logit_softcap = float(logit_scale), float(logit_softcap or 0.0)
         self.stream_dtype = stream_dtype
         self.embedding, self.layers, self.final_norm, self.head = embedding, list(layers), final_norm, head
         self.order = [call if isinstance(call, LayerCall) else LayerCall(*call) for call in order]
@@ -96,13 +100,20 @@ class DecoderModel(Part):
         CUDA graphs cuts there, so that the GPU starts on the first layers while the rest is
         still being submitted.
         """
+        ctx.extras.pop("pending_join", None)         # nothing of a step that failed half-way joins this one
         x = self.embedding.forward(ctx, ctx.token_ids)
         for index, call in enumerate(self.order):
             if checkpoint is not None and index and index % calls_per_checkpoint == 0:
                 checkpoint()
-            x = self.layers[call.layer].forward(ctx, x, cache_views[index])
+            block = self.layers[call.layer]
+            if not getattr(block, "takes_pending_join", False):
+                settle_stream(ctx)
+            x = block.forward(ctx, x, cache_views[index])
+        settle_stream(ctx)
         if logit_rows is None or logit_rows.shape[0] == 0:
             return None
         normed = self.final_norm.forward(ctx, x, rows=logit_rows)
         logits = self.head.forward(ctx, normed, out_float32=True)
-        return ops.scale_inplace(logits, self.logit_scale) if self.logit_scale != 1.0 else logits
+        if self.logit_scale != 1.0:
+            ops.scale_inplace(logits, self.logit_scale)
+        return ops.softcap_inplace(logits, self.logit_softcap) if self.logit_softcap else logits

@@ -15,7 +15,8 @@ Options for other designs of routing:
 
 ``routing="softmax_all"``  scores = softmax over all outputs of the router; the choice goes by score + a stored
                            correction (``names["correction"]``), the weights are the chosen scores themselves,
-                           divided by their sum (+ 1e-20) and multiplied by ``weight_scale``
+                           divided by their sum (+ 1e-20) and multiplied by ``weight_scale``;
+                           ``renormalize=False`` leaves out the division: the chosen scores are the weights
 ``identity``               so many further outputs of the router, behind the experts', name no expert: a token
                            that chooses one gets weight * x, its own input
 ``gated=False``            experts without a gate matrix: down_e(act(up_e x)), ``activation`` one without a gate
@@ -37,7 +38,8 @@ class RoutedExperts(FeedForward):
     graph_safe = True
 
     def __init__(self, hidden_size, expert_size, n_experts, top, *, names, activation="silu", limit=0.0, alpha=1.0,
-                 shared=None, routing="softmax_chosen", weight_scale=1.0, identity=0, gated=True, shared_gate=None):
+                 shared=None, routing="softmax_chosen", weight_scale=1.0, identity=0, gated=True, shared_gate=None,
+                 renormalize=True):
         self.hidden_size, self.expert_size = int(hidden_size), int(expert_size)
         self.n_experts, self.top, self.identity = int(n_experts), int(top), int(identity)
         if self.identity < 0 or not 1 <= self.top <= self.n_experts + self.identity:
@@ -48,6 +50,9 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"activation {activation!r} does not fit experts {'with' if gated else 'without'} a gate matrix")
         self.activation, self.limit, self.alpha = activation, float(limit), float(alpha)
         self.routing, self.weight_scale, self.gated = routing, float(weight_scale), bool(gated)
+        self.renormalize = bool(renormalize)
+        if not self.renormalize and routing != "softmax_all":
+            raise ValueError("only the scores of a softmax over all outputs can weigh the experts undivided")
         self.shared = shared
         outputs = self.n_experts + self.identity
         self.router = Param((outputs, hidden_size), std=0.5)
@@ -96,7 +101,13 @@ class RoutedExperts(FeedForward):
 
     takes_out_scale = True
 
-    def forward(self, ctx, x, residual=None, out_scale=None):
+    def forward(self, ctx, x, residual=None, out_scale=None, out_float32=False):
+        """``out_float32``: the experts' weighted sum as float32 rows (for a block that norms the branch before it
+        joins the stream); without it and without a residual the result has the stream's dtype."""
+        if out_float32:
+            if residual is not None or out_scale is not None:
+                raise ValueError("a float32 result goes without a residual")
+            return self._forward_general(ctx, x, None, None, torch.float32)
         if self.routing == "softmax_all" or self.identity or not self.gated or self.shared_gate is not None \
                 or out_scale is not None:
             return self._forward_general(ctx, x, residual, out_scale)
@@ -108,17 +119,18 @@ class RoutedExperts(FeedForward):
             out = self.shared.forward(ctx, x, residual=out)
         return out
 
-    def _forward_general(self, ctx, x, residual, out_scale):
+    def _forward_general(self, ctx, x, residual, out_scale, out_dtype=None):
         """Every option at once: the shared expert's float32 output, its gate and the output scale go into the
         kernel that sums a token's experts onto the residual."""
         routed = ops.moe_route(x, self._router, self.router_bias.data if self.router_bias else None, self.top,
                                softmax_all=self.routing == "softmax_all",
                                correction=self.correction.data if self.correction is not None else None,
-                               weight_scale=self.weight_scale, gate_row=self.shared_gate is not None)
+                               weight_scale=self.weight_scale, gate_row=self.shared_gate is not None,
+                               renormalize=self.renormalize)
         chosen, weights = routed[:2]
         extra = self.shared.forward(ctx, x, out_float32=True) if self.shared is not None else None
         first, second = (self._gate, self._up) if self.gated else (self._up, None)
         return ops.moe_experts(x, chosen, weights, first, second, self._down, self.activation, limit=self.limit,
                                alpha=self.alpha, residual=residual, identity=self.identity > 0, extra=extra,
                                extra_gate=routed[2] if self.shared_gate is not None else None, col_scale=out_scale,
-                               out=None if residual is not None else ctx.empty(x.shape, dtype=ctx.stream_dtype))
+                               out=None if residual is not None else ctx.empty(x.shape, dtype=out_dtype or ctx.stream_dtype))

@@ -18,6 +18,11 @@ window; ``ops.head_product`` again (the sum through Wuv, times the gate); the ou
 than ``LIBRARY_ROWS`` tokens hands the two per-head products to the library as batched products over strided views
 of the same buffers (as ``Linear`` does with its products), and ``ops.head_gate`` applies the gates.
 
+Options for other designs of the same mixer: no rotated part at all (``rot_dim`` 0, ``position`` None); queries that
+come through a latent of their own (``query_latent``: c_q = rms(Wdq h) w, q = Wuq c_q, with Wdq's rows in the stacked
+projection, the norm over that column range and Wuq a product of its own); a learned sink (``sink="learned"``: exp(s_a)
+joins head a's denominator; no window then); a gate per output element instead of one per head (``gate="element"``).
+
 A page holds one row per token, the key [z, rot(s)]; the token's value z is that row's first c columns (the cache's
 shared rows), so the attention kernels fetch one tile per 64 positions and use it for the scores and for the
 weighted sum alike.  Where c + r is a head size the tensor-core attention takes (a multiple of 16 up to 256) a
@@ -40,37 +45,58 @@ LIBRARY_ROWS = 64      # bfloat16 steps of more tokens than this run the per-hea
 
 class LatentAttention(Mixer):
     """names: dict with keys q, dkv, dkv_norm, uk, uv, g, o (tensor names; ``suffixes`` are appended to the
-    projections', ``norm_suffix`` to the norm's).  ``position``: a :class:`RotaryFrequencies` over the rotated part."""
+    projections', ``norm_suffix`` to the norms'); with ``query_latent`` (the latent's size) dq, dq_norm and uq in place of
+    q; with a learned sink also sink.  ``position``: a :class:`RotaryFrequencies` over the rotated part."""
     graph_safe = True
 
     def __init__(self, hidden_size, n_heads, plain_dim, rot_dim, value_dim, latent_dim, *, scale, window, position,
-                 norm_eps, names, suffixes=(".weight", ".bias"), norm_suffix=".weight"):
+                 norm_eps, names, suffixes=(".weight", ".bias"), norm_suffix=".weight", query_latent=0, sink=None,
+                 gate="head"):
         self.hidden_size, self.n_heads = int(hidden_size), int(n_heads)
         self.plain_dim, self.rot_dim, self.value_dim, self.latent_dim = int(plain_dim), int(rot_dim), int(value_dim), int(latent_dim)
         self.scale, self.window, self.norm_eps = float(scale), int(window or 0), float(norm_eps)
-        if not isinstance(position, RotaryFrequencies) or position.rotary_dim > self.rot_dim:
+        if self.rot_dim == 0 and position is None:
+            pass                                       # keys without a rotated part: no positions at all
+        elif not isinstance(position, RotaryFrequencies) or position.rotary_dim > self.rot_dim:
             raise ValueError("latent attention rotates by frequencies, over at most its rotated dimensions")
+        if sink not in (None, "learned") or gate not in ("head", "element"):
+            raise ValueError(f"latent attention: sink {sink!r} (None or 'learned'), gate {gate!r} ('head' or 'element')")
+        if sink and self.window:
+            raise ValueError("a sink goes without a window")
+        self.query_latent, self.learned_sink, self.gate_each = int(query_latent or 0), sink == "learned", gate == "element"
+        if self.query_latent and self.rot_dim:
+            raise ValueError("queries through a latent go without a rotated part")
         self.position = position
         self.key_width = self.latent_dim + self.rot_dim
         # the width of a bfloat16 step's attended rows: see the module's text
         self.value_width = self.key_width if attention_mma.supports(self.key_width, 1, 1) else self.latent_dim
         q_width = self.n_heads * (self.plain_dim + self.rot_dim)
-        self.projection = StackedLinear(hidden_size, [(names["q"], q_width), (names["dkv"], self.key_width),
-                                                      (names["g"], self.n_heads)], suffixes=suffixes)
-        self.columns = (0, q_width, q_width + self.key_width)
+        first = (names["dq"], self.query_latent) if self.query_latent else (names["q"], q_width)
+        gates = self.n_heads * (self.value_dim if self.gate_each else 1)
+        self.projection = StackedLinear(hidden_size, [first, (names["dkv"], self.key_width), (names["g"], gates)],
+                                        suffixes=suffixes)
+        self.columns = (0, first[1], first[1] + self.key_width)
         self.latent_norm = Param((self.latent_dim,), init="norm", std=0.05)
         self.key_up = Param((self.n_heads * self.plain_dim, self.latent_dim))
         self.value_up = Param((self.n_heads * self.value_dim, self.latent_dim))
         self._names = {names["dkv_norm"] + norm_suffix: self.latent_norm, names["uk"] + suffixes[0]: self.key_up,
                        names["uv"] + suffixes[0]: self.value_up}
+        self.query_norm = self.query_up = self.sink_logits = None
+        if self.query_latent:
+            self.query_norm = Param((self.query_latent,), init="norm", std=0.05)
+            self._names[names["dq_norm"] + norm_suffix] = self.query_norm
+            self.query_up = Linear(self.query_latent, q_width, name=names["uq"], suffixes=suffixes)
+        if self.learned_sink:
+            self.sink_logits = Param((self.n_heads,), std=1.0)
+            self._names[names["sink"]] = self.sink_logits
         self.out = Linear(self.n_heads * self.value_dim, hidden_size, name=names["o"], suffixes=suffixes)
-        self._query_fold = self._value_unfold = None
+        self._query_fold = self._value_unfold = self._options = self._sinks = None
 
     def named_params(self):
         return dict(self._names)
 
     def children(self):
-        return [self.projection, self.out, self.position]
+        return [part for part in (self.projection, self.query_up, self.out, self.position) if part is not None]
 
     def finalize(self, device, dtype):
         super().finalize(device, dtype)
@@ -81,6 +107,11 @@ class LatentAttention(Mixer):
         self._value_unfold = self.value_up.data.to(common).view(self.n_heads, self.value_dim, self.latent_dim).contiguous()
         self.key_up.data = self.value_up.data = None
         self.latent_norm.data = self.latent_norm.data.to(common).contiguous()
+        if self.query_norm is not None:
+            self.query_norm.data = self.query_norm.data.to(common).contiguous()
+        if self.sink_logits is not None:           # the softmax runs in float32 whatever the activations are
+            self._sinks = self.sink_logits.data.float().contiguous()
+            self._options = attention_mma.ScoreOptions(sink_logits=self._sinks)
 
     def step_planners(self):
         return {**super().step_planners(), _PLANNER.key: _PLANNER}
@@ -91,7 +122,13 @@ class LatentAttention(Mixer):
     def forward(self, ctx, x, cache, residual=None, out_float32=False):
         """x [N, hidden] -> [N, hidden] (+ residual); ``cache`` is a KVCacheView of rows [latent, rotated key part]."""
         projected = self.projection.forward(ctx, x)
-        queries = self.prepare(ctx, projected, cache)
+        source = None
+        if self.query_latent:
+            # the queries' own latent: the norm over its columns of the stacked product, then the expansion
+            latent = ops.rmsnorm_exact(projected, self.query_norm.data, self.norm_eps, out_dtype=ctx.dtype,
+                                       columns=(self.columns[0], self.query_latent))
+            source = self.query_up.forward(ctx, latent)
+        queries = self.prepare(ctx, projected, cache, source)
         attended = self.attend(ctx, queries, cache)
         mixed = self.expand(ctx, attended, projected)
         return self.out.forward(ctx, mixed, residual=residual, out_float32=out_float32)
@@ -100,21 +137,25 @@ class LatentAttention(Mixer):
         return projected.shape[0] > LIBRARY_ROWS and projected.dtype == torch.bfloat16 \
             and self._query_fold.dtype == torch.bfloat16
 
-    def prepare(self, ctx, projected, cache):
+    def prepare(self, ctx, projected, cache, source=None):
         """The projection's tail: the token's key row into its page, the queries [N, H * (c + r)] as the attention
-        reads them (plain part through Wuk^T, rotated part turned)."""
+        reads them (plain part through Wuk^T, rotated part turned).  ``source``: the queries [N, H * d] where they
+        are not the projection's first columns (queries that came through a latent of their own)."""
         n, heads, width = projected.shape[0], self.n_heads, self.key_width
         queries = ctx.empty((n, heads * width))
         rotation = self.position
         ops.latent_prepare(projected, self.columns[0], self.columns[1], queries, cache.pages, self.latent_norm.data,
-                           self.norm_eps, rotation.freq, rotation.rotary_dim, rotation.layout, ctx.positions, ctx.token_row,
+                           self.norm_eps, rotation.freq if rotation is not None else None,
+                           rotation.rotary_dim if rotation is not None else 0,
+                           rotation.layout if rotation is not None else 0, ctx.positions, ctx.token_row,
                            cache.block_table, heads, self.plain_dim, self.rot_dim, self.latent_dim, 0, cache.page_size)
+        q_rows, q_width = (projected, self.columns[1]) if source is None else (source, source.shape[1])
         if self._batched(projected):
-            plain = projected[:, :self.columns[1]].unflatten(1, (heads, self.plain_dim + self.rot_dim))[:, :, :self.plain_dim]
+            plain = q_rows[:, :q_width].unflatten(1, (heads, self.plain_dim + self.rot_dim))[:, :, :self.plain_dim]
             torch.bmm(plain.transpose(0, 1), self._query_fold.transpose(1, 2),
                       out=queries.view(n, heads, width)[:, :, :self.latent_dim].transpose(0, 1))
         else:
-            ops.head_product(projected, self.columns[0], self.plain_dim + self.rot_dim, self._query_fold, queries, 0, width)
+            ops.head_product(q_rows, 0, self.plain_dim + self.rot_dim, self._query_fold, queries, 0, width)
         return queries
 
     def attend(self, ctx, queries, cache):
@@ -123,12 +164,13 @@ class LatentAttention(Mixer):
         n, heads, width = queries.shape[0], self.n_heads, self.key_width
         if queries.dtype == torch.bfloat16 and self.value_width == width:
             attended = ctx.empty((n, heads * width))
-            attention_mma.attend(ctx, queries, cache, attended, heads, 1, width, self.window, self.scale, shared_rows=True,
-                                 value_cols=self.latent_dim)
+            attention_mma.attend(ctx, queries, cache, attended, heads, 1, width, self.window, self.scale,
+                                 options=self._options, shared_rows=True, value_cols=self.latent_dim)
         else:
             attended = ctx.empty((n, heads * self.latent_dim))
             ops.attention_generic(queries, cache.pages, attended, ctx.positions, ctx.token_row, cache.block_table, heads, 1,
-                                  width, cache.page_size, self.window, self.scale, v_dim=self.latent_dim, shared_rows=True)
+                                  width, cache.page_size, self.window, self.scale, v_dim=self.latent_dim, shared_rows=True,
+                                  sink=self.learned_sink, sink_logits=self._sinks)
         return attended
 
     def expand(self, ctx, attended, projected):
@@ -140,8 +182,8 @@ class LatentAttention(Mixer):
             sums = attended.view(n, heads, stride)[:, :, :self.latent_dim]
             torch.bmm(sums.transpose(0, 1), self._value_unfold.transpose(1, 2),
                       out=mixed.view(n, heads, self.value_dim).transpose(0, 1))
-            ops.head_gate(mixed, self.value_dim, projected, self.columns[2])
+            ops.head_gate(mixed, 1 if self.gate_each else self.value_dim, projected, self.columns[2])
         else:
             ops.head_product(attended, 0, stride, self._value_unfold, mixed, 0, self.value_dim,
-                             gate=projected, gate_column=self.columns[2])
+                             gate=projected, gate_column=self.columns[2], gate_each=self.gate_each)
         return mixed

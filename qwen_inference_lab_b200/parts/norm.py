@@ -52,20 +52,25 @@ class ExactRMSNorm(Norm):
 class LayerNorm(Norm):
     """``y = (x - mean) / sqrt(var + eps) * w + b`` with ``var`` the mean of the squared deviations: float32
     arithmetic and a single rounding, like :class:`ExactRMSNorm`, and like it it may read a float32 residual
-    stream under bfloat16 activations.  ``suffixes``: what the checkpoint appends to ``name`` for weight and bias."""
+    stream under bfloat16 activations.  ``suffixes``: what the checkpoint appends to ``name`` for weight and bias.
+    ``bias=False``: a layer norm with a weight alone."""
     graph_safe = True
 
-    def __init__(self, width, eps, *, name, suffixes=(".weight", ".bias"), optional=False):
+    def __init__(self, width, eps, *, name, suffixes=(".weight", ".bias"), optional=False, bias=True):
         self.width, self.eps, self.name, self.suffixes = int(width), float(eps), name, tuple(suffixes)
         self.weight = Param((width,), init="norm", std=0.05, optional=optional)
-        self.bias = Param((width,), init="normal", std=0.05, optional=optional)
+        self.bias = Param((width,), init="normal", std=0.05, optional=optional) if bias else None
 
     def named_params(self):
-        return {self.name + self.suffixes[0]: self.weight, self.name + self.suffixes[1]: self.bias}
+        params = {self.name + self.suffixes[0]: self.weight}
+        if self.bias is not None:
+            params[self.name + self.suffixes[1]] = self.bias
+        return params
 
     def finalize(self, device, dtype):
-        if self.weight.data is not None and self.bias.data.dtype != self.weight.data.dtype:
+        if self.bias is not None and self.weight.data is not None and self.bias.data.dtype != self.weight.data.dtype:
             self.bias.data = self.bias.data.to(self.weight.data.dtype)
 
     def forward(self, ctx, x, rows=None):
-        return ops.layernorm_exact(x, self.weight.data, self.bias.data, self.eps, out_dtype=ctx.dtype, rows=rows)
+        return ops.layernorm_exact(x, self.weight.data, self.bias.data if self.bias is not None else None, self.eps,
+                                   out_dtype=ctx.dtype, rows=rows)

@@ -10,6 +10,8 @@ another table.
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import PositionEncoding
@@ -42,18 +44,42 @@ class RotaryFrequencies(PositionEncoding):
     ``float(p) * freq[i]`` with ``freq[i] = base^(-2 i / dims)``, i < dims / 2.  No table: a request may be as long
     as the cache allows.  ``layout`` says which of the ``dims`` rotated dimensions of a vector pair up:
     ``"halves"`` (i with i + dims / 2) or ``"interleaved"`` (2 i with 2 i + 1); dimensions from ``dims`` on pass
-    unchanged.  The frequencies are made on the host in float64 and rounded once to float32."""
+    unchanged.  The frequencies are made on the host in float64 and rounded once to float32.
+
+    ``scaling`` = (factor, low, high, original) stretches long waves for contexts beyond the ``original`` one: with
+    wavelength l = 2 pi / freq, a frequency stays when l < original / high, becomes freq / factor when
+    l > original / low, and between the two is (1 - s) freq / factor + s freq with
+    s = (original / l - low) / (high - low)."""
     graph_safe = True
     LAYOUTS = {"halves": 0, "interleaved": 1}
 
-    def __init__(self, dims, base, layout="halves"):
+    def __init__(self, dims, base, layout="halves", scaling=None):
         if dims % 2 or dims <= 0:
             raise ValueError(f"the number of rotated dimensions must be positive and even, got {dims}")
         if layout not in self.LAYOUTS:
             raise ValueError(f"unknown rotary layout {layout!r} (known: {sorted(self.LAYOUTS)})")
         self.rotary_dim, self.base, self.layout = int(dims), float(base), self.LAYOUTS[layout]
+        self.scaling = None if scaling is None else tuple(float(v) for v in scaling)
+        if self.scaling is not None and (len(self.scaling) != 4 or self.scaling[0] <= 0 or self.scaling[3] <= 0
+                                         or not 0 < self.scaling[1] < self.scaling[2]):
+            raise ValueError(f"frequency scaling wants (factor, low, high, original) with 0 < low < high, got {scaling}")
         self.freq = None
 
-    def finalize(self, device, dtype):
+    def frequencies(self) -> list:
+        """The frequency of every rotated pair as Python floats (float64)."""
         values = [self.base ** (-2.0 * i / self.rotary_dim) for i in range(self.rotary_dim // 2)]
+        if self.scaling is None:
+            return values
+        factor, low, high, original = self.scaling
+        for i, f in enumerate(values):
+            wave = 2.0 * math.pi / f
+            if wave > original / low:
+                values[i] = f / factor
+            elif wave >= original / high:
+                s = (original / wave - low) / (high - low)
+                values[i] = (1.0 - s) * f / factor + s * f
+        return values
+
+    def finalize(self, device, dtype):
+        values = self.frequencies()
         self.freq = torch.tensor(values, dtype=torch.float64).to(torch.float32).to(device)
