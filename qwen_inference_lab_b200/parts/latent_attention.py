@@ -69,7 +69,8 @@ class LatentAttention(Mixer):
         self.position = position
         self.key_width = self.latent_dim + self.rot_dim
         # the width of a bfloat16 step's attended rows: see the module's text
-        self.value_width = self.key_width if attention_mma.supports(self.key_width, 1, 1) else self.latent_dim
+        self.tensor_cores = attention_mma.supports(self.key_width, 1, 1)
+        self.value_width = self.key_width if self.tensor_cores else self.latent_dim
         q_width = self.n_heads * (self.plain_dim + self.rot_dim)
         first = (names["dq"], self.query_latent) if self.query_latent else (names["q"], q_width)
         gates = self.n_heads * (self.value_dim if self.gate_each else 1)
@@ -162,7 +163,7 @@ class LatentAttention(Mixer):
         """Every head over the one key row per token: per head a row whose first c columns are the weighted sum of
         latents, [N, H * (c + r)] from the tensor-core kernels and [N, H * c] from the float32 kernel."""
         n, heads, width = queries.shape[0], self.n_heads, self.key_width
-        if queries.dtype == torch.bfloat16 and self.value_width == width:
+        if queries.dtype == torch.bfloat16 and self.tensor_cores:
             attended = ctx.empty((n, heads * width))
             attention_mma.attend(ctx, queries, cache, attended, heads, 1, width, self.window, self.scale,
                                  options=self._options, shared_rows=True, value_cols=self.latent_dim)

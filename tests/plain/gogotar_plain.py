@@ -155,10 +155,14 @@ def route(h, router, top, low=None):
     return order, torch.gather(scores, 1, order)
 
 
-def routed_experts(h, w, prefix, mlp, low=None):
-    """sum over a token's chosen experts of score_e * down_e(silu(gate_e h) * (up_e h))."""
+def routed_experts(h, w, prefix, mlp, low=None, margins=None):
+    """sum over a token's chosen experts of score_e * down_e(silu(gate_e h) * (up_e h)).  ``margins``: a list that
+    receives, per token, by how much of itself the last chosen score leads the first rejected one."""
     top = mlp["router"]["top"]
     chosen, weights = route(h, w[prefix + "router"], top, low)
+    if margins is not None and top < mlp["router"]["experts"]:
+        ranked = torch.softmax(h @ w[prefix + "router"].to(h.dtype).t(), dim=-1).sort(dim=-1, descending=True).values
+        margins.append((ranked[:, top - 1] - ranked[:, top]) / ranked[:, top - 1])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for n in range(top):
@@ -180,8 +184,9 @@ def layer_runs(config):
     return list(range(start)) + list(range(start, stop)) * times + list(range(stop, count))
 
 
-def forward(config, w, tokens, dtype=torch.float64, low=None, return_layers=False):
-    """Logits [T, vocab] of a whole sequence (and the residual stream after every layer run)."""
+def forward(config, w, tokens, dtype=torch.float64, low=None, return_layers=False, margins=None):
+    """Logits [T, vocab] of a whole sequence (and the residual stream after every layer run).  ``margins``: a list
+    that receives every routed layer run's margins (see ``routed_experts``)."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     eps = config["norm"]["eps"]
     x = w["embed"][tokens].to(dtype) * config["embedding"]["scale"]
@@ -193,8 +198,11 @@ def forward(config, w, tokens, dtype=torch.float64, low=None, return_layers=Fals
         x = x + layer_norm(y, w[p + "norm1b"], eps)
         mlp = layer.get("mlp")
         if mlp is not None:
-            ff = clamped_feed_forward if mlp["kind"] == "dense" else routed_experts
-            y = ff(_round(layer_norm(x, w[p + "norm2"], eps), low), w, p + "mlp.", mlp, low)
+            inputs = _round(layer_norm(x, w[p + "norm2"], eps), low)
+            if mlp["kind"] == "dense":
+                y = clamped_feed_forward(inputs, w, p + "mlp.", mlp, low)
+            else:
+                y = routed_experts(inputs, w, p + "mlp.", mlp, low, margins)
             x = x + layer_norm(y, w[p + "norm2b"], eps)
         after.append(x.clone())
     h = _round(layer_norm(x, w["final.norm"], eps), low)
