@@ -1092,6 +1092,193 @@ def run_larolorn(args):
         torch.cuda.empty_cache()
 
 
+# --------------------------------------------------------------------------- Gogotar beside Larolorn
+def _gogotar_sizes(width, heads, kv_heads, dim, rank, rot, ff, span, vocab, **_):
+    """Six layers of which the middle two run twice (eight layer runs): latent attention with a dense feed-forward and
+    chunked attention with routed experts in turn.  The latent's key row is as wide as Larolorn's (latent + rotated
+    part there); an expert is a quarter of the dense feed-forward and a token uses four of thirty-two."""
+    latent = dict(heads=heads, dim=dim, vdim=dim, kv_rank=rank + rot, q_rank=4 * (rank + rot), scale=dim ** -0.5)
+    attention = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, softcap=50.0, mask=dict(size=span),
+                     rot=dict(base=500000.0, dims=dim // 2, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    one = dict(type="latent_attention", mixer=latent, mlp=dict(kind="dense", ff=ff, limit=7.0))
+    two = dict(type="attention", mixer=attention, mlp=dict(kind="moe", expert=dict(ff=ff // 4), router=dict(experts=32, top=4)))
+    return dict(architecture="Gogotar", vocab=vocab, width=width, norm=dict(eps=1e-6), embedding=dict(scale=4.0),
+                logit_softcap=30.0, loop=dict(start=2, stop=4, times=2), layers=[one, two, one, two, one, two])
+
+
+def _gogotar_kernels(torch, gogotar, larolorn, sizes, pk, tokens_n, batch, context, flush):
+    """The kernels of Gogotar's mechanisms alone, each beside the like kernel of Larolorn (of Virulix for the routed
+    experts, which Larolorn has none of), with what the roofline allows."""
+    from qwen_inference_lab_b200.kernels import ops
+    from qwen_inference_lab_b200.parts import RoutedExperts
+    bench = _PartKernels(torch, pk, tokens_n, batch, context, flush)
+    H, G, d, W = sizes["heads"], sizes["kv_heads"], sizes["dim"], sizes["width"]
+    span = sizes["span"]
+    ours_latent = next(l.mixer for l in gogotar.layers if hasattr(l.mixer, "latent_dim"))
+    ours_attention = next(l.mixer for l in gogotar.layers if hasattr(l.mixer, "values_from_keys"))
+    their_latent = next(l.mixer for l in larolorn.layers if hasattr(l.mixer, "latent_dim"))
+    their_attention = next(l.mixer for l in larolorn.layers if hasattr(l.mixer, "left")).left
+    pairs_window = sum(min(i, span - 1) + 1 for i in range(tokens_n))
+    pairs_chunk = sum(i % span + 1 for i in range(tokens_n))
+    pairs_all = tokens_n * (tokens_n + 1) // 2
+
+    # ---- attention itself
+    def latent_attention(latent):
+        row = latent.key_width
+        def kernel(ctx, x, view):
+            q = x[:, :H * row].contiguous()
+            return bench.timed(lambda: latent.attend(ctx, q, view))
+        return kernel
+    row = ours_latent.key_width
+    bench.measure(f"gogotar latent attention (one key row of {row} for {H} heads, causal, sinks)", ours_latent, H * row,
+                  latent_attention(ours_latent), (4.0 * H * row * pairs_all, None), batch * (context + 1) * row * 2)
+    row = their_latent.key_width
+    bench.measure(f"larolorn latent attention (one key row of {row}, window)", their_latent, H * row,
+                  latent_attention(their_latent), (2.0 * H * (row + their_latent.latent_dim) * pairs_window, None),
+                  batch * min(context + 1, span) * row * 2)
+    def grouped_attention(mixer):
+        def kernel(ctx, x, view):
+            q = x[:, :H * d].contiguous()
+            out = torch.empty_like(q)
+            bench.timed(lambda: mixer._attend(ctx, q, view, out))
+            return out
+        return kernel
+    for label, mixer in (("gogotar chunked attention (capped scores, learned sinks)", ours_attention),
+                         ("larolorn chunked attention (learned sinks)", their_attention)):
+        bench.measure(label, mixer, H * d, grouped_attention(mixer), (4.0 * H * d * pairs_chunk, None),
+                      batch * (context % span + 1) * 2 * G * d * 2)
+
+    # ---- what stands between the projection and the attention
+    moved = lambda n, width: 2 * n * width * 2          # every row read once and written once
+    def rotate_store(mixer, channels, per_head):
+        q_weight, k_weight = (mixer.q_norm, mixer.k_norm) if per_head else (mixer.whole_q_norm, mixer.whole_k_norm)
+        eps = mixer.qk_norm_eps if per_head else mixer.whole_qk_norm_eps
+        def kernel(ctx, x, view):
+            qkv = x[:, :channels].contiguous()
+            q = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)
+            bench.timed(lambda: ops.qk_rotate_store(qkv, (0, H * d, H * d if per_head else (H + G) * d), q, view.pages,
+                                                    q_weight.data, k_weight.data, eps, mixer.position.freq,
+                                                    mixer.position.rotary_dim, mixer.position.layout, ctx.positions,
+                                                    ctx.token_row, view.block_table, H, G, d, d, view.page_size,
+                                                    per_head=per_head))
+            return q
+        return kernel
+    channels = (H + G) * d
+    bench.measure("gogotar per-head norms + rotation + page write (keys as values)", ours_attention, channels,
+                  rotate_store(ours_attention, channels, True), (None, moved(tokens_n, channels) + tokens_n * G * d * 2),
+                  moved(batch, channels))
+    channels = (H + 2 * G) * d
+    bench.measure("larolorn whole-projection norms + rotation + page write", their_attention, channels,
+                  rotate_store(their_attention, channels, False), (None, moved(tokens_n, channels)), moved(batch, channels))
+    def head_gates(ctx, x, view):
+        attended = x[:, :H * d].contiguous()
+        gates = x[:, :H].contiguous()
+        return bench.timed(lambda: ops.head_gate(attended, d, gates, 0))
+    bench.measure("gogotar gate per head on the attention's output", ours_attention, H * d, head_gates,
+                  (None, moved(tokens_n, H * d)), moved(batch, H * d))
+    stacked = ours_latent.projection.out_features
+    def our_latent_tail(ctx, x, view):
+        projected = x[:, :stacked].contiguous()
+        def tail():
+            latent = ops.rmsnorm_exact(projected, ours_latent.query_norm.data, ours_latent.norm_eps, out_dtype=ctx.dtype,
+                                       columns=(0, ours_latent.query_latent))
+            return ours_latent.prepare(ctx, projected, view, ours_latent.query_up.forward(ctx, latent))
+        return bench.timed(tail)
+    fold = 2.0 * H * ours_latent.plain_dim * (ours_latent.latent_dim + ours_latent.query_latent)
+    bench.measure("gogotar query latent norm + expansion, latent norm + page write, queries through the key expansion",
+                  ours_latent, stacked, our_latent_tail, (fold * tokens_n, None),
+                  batch * (stacked + H * ours_latent.key_width) * 2 + H * ours_latent.plain_dim * (ours_latent.latent_dim + ours_latent.query_latent) * 2)
+    their_stacked = their_latent.projection.out_features
+    def their_latent_tail(ctx, x, view):
+        projected = x[:, :their_stacked].contiguous()
+        return bench.timed(lambda: their_latent.prepare(ctx, projected, view))
+    bench.measure("larolorn latent norm + rotation + page write, queries through the key expansion", their_latent,
+                  their_stacked, their_latent_tail, (2.0 * H * their_latent.plain_dim * their_latent.latent_dim * tokens_n, None),
+                  batch * (their_stacked + H * their_latent.key_width) * 2 + H * their_latent.plain_dim * their_latent.latent_dim * 2)
+    def latent_values(latent, width):
+        def kernel(ctx, x, view):
+            attended = x[:, :H * latent.value_width].contiguous()
+            projected = x[:, :width].contiguous()
+            return bench.timed(lambda: latent.expand(ctx, attended, projected))
+        return kernel
+    for label, latent, width in (("gogotar value expansion with a gate per element", ours_latent, stacked),
+                                 ("larolorn value expansion with the head gates", their_latent, their_stacked)):
+        bench.measure(label, latent, max(width, H * latent.value_width), latent_values(latent, width),
+                      (2.0 * H * latent.value_dim * latent.latent_dim * tokens_n, None),
+                      batch * H * (latent.value_width + latent.value_dim) * 2 + H * latent.value_dim * latent.latent_dim * 2)
+
+    # ---- joining the stream
+    block = gogotar.layers[0]
+    def norm_join(ctx, x, view):
+        stream, branch = x[:, :W].float(), x[:, :W].float() * 3.0
+        rows = torch.empty((x.shape[0], W), dtype=x.dtype, device=x.device)
+        return bench.timed(lambda: ops.norm_join(stream, branch, block.post1.data, block.eps, "layer", next_weight=block.pre2.data,
+                                                 rows=rows))
+    join_bytes = lambda n: n * W * (4 * 3 + 2)           # the stream read and written, a float32 branch read, rows written
+    bench.measure("gogotar a layer-normed branch joins the stream, the next layer norm behind it (1 kernel)", ours_latent, W,
+                  norm_join, (None, join_bytes(tokens_n)), join_bytes(batch))
+    their_block = larolorn.layers[0]
+    def rms_join(ctx, x, view):
+        stream, branch = x[:, :W].float(), x[:, :W].float() * 3.0
+        rows = torch.empty((x.shape[0], W), dtype=x.dtype, device=x.device)
+        return bench.timed(lambda: ops.rms_join(stream, branch, their_block.mixer_norm.data, their_block.eps, 0.5, rows=rows))
+    bench.measure("larolorn a normed branch joins the stream, its rounded copy behind it (1 kernel)", their_latent, W,
+                  rms_join, (None, join_bytes(tokens_n)), join_bytes(batch))
+
+    # ---- routed experts, beside routed experts that renormalise the chosen logits (Virulix's)
+    def feed_forward(part, **how):
+        def kernel(ctx, x, view):
+            h = x[:, :W].contiguous()
+            return bench.timed(lambda: part.forward(ctx, h, **how))
+        return kernel
+    ours = next(l.feed_forward for l in gogotar.layers if hasattr(l.feed_forward, "n_experts"))
+    names = dict(router="r", router_bias=None, expert=lambda index, which: f"e{index}.{which}")
+    theirs = RoutedExperts(W, ours.expert_size, ours.n_experts, ours.top, names=names, activation="silu")
+    for param in theirs.all_named_params().values():
+        param.data = (torch.randn(param.shape, device="cuda") * 0.02).to(torch.bfloat16)
+    theirs.finalize(torch.device("cuda"), torch.bfloat16)
+    active = 3 * ours.expert_size * W
+    touched = lambda n: min(ours.n_experts, n * ours.top) * active * 2
+    bench.measure("gogotar routed experts (softmax over all, unrenormalised, float32 result)", ours, W,
+                  feed_forward(ours, out_float32=True), (2.0 * tokens_n * ours.top * active, None), touched(batch))
+    bench.measure("virulix-style routed experts (softmax over the chosen)", theirs, W, feed_forward(theirs),
+                  (2.0 * tokens_n * ours.top * active, None), touched(batch))
+    return bench.rows
+
+
+def run_gogotar(args):
+    """Prefill and decode of Gogotar at sizes like a real model's layers, beside Larolorn (the engine's closest design: a
+    float32 stream, latent attention, chunked attention with learned sinks, clamped feed-forwards, branches normed on
+    their way into the stream) of equal width, heads, layer runs, key row, feed-forward size and vocabulary, and the
+    kernels of its mechanisms against their rooflines."""
+    import torch
+    from qwen_inference_lab_b200.config.model_config import GogotarConfig, LarolornConfig
+    from qwen_inference_lab_b200.loading import random_model
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for name in ([args.gogotar_shape] if args.gogotar_shape else sorted(LAROLORN_SHAPES)):
+        sizes = LAROLORN_SHAPES[name]
+        gogotar = random_model(GogotarConfig.from_dict(_gogotar_sizes(**sizes)), seed=0, device="cuda", dtype=torch.bfloat16)
+        larolorn = random_model(LarolornConfig.from_dict(_larolorn_sizes(**sizes)), seed=0, device="cuda", dtype=torch.bfloat16)
+        result = {"workload": "gogotar", "width": sizes["width"], "layer_runs": 8, "dtype": "bfloat16",
+                  "peaks": "of measured" if pk["source"] == "measured" else "of fallback", "models": {}, "kernels": []}
+        for label, model in (("gogotar", gogotar), ("larolorn", larolorn)):
+            bench = _ModelBench(model, sizes["vocab"])
+            entry = {}
+            for tokens_n in (512, 2048):
+                ms = bench.prefill(tokens_n, flush)
+                entry[f"prefill_{tokens_n}"] = {"ms": round(ms, 3), "tokens_per_s": round(tokens_n / ms * 1e3, 1)}
+            for batch, context in ((1, 2048), (8, 2048), (32, 2048)):
+                ms = bench.decode(batch, context, args.steps, max(args.warmup, 6))
+                entry[f"decode_b{batch}_c{context}"] = {"ms": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3, 1)}
+            result["models"][label] = entry
+        for kernel, ms, frac, of in _gogotar_kernels(torch, gogotar, larolorn, sizes, pk, 2048, 8, 2048 + 511, flush):
+            result["kernels"].append({"kernel": kernel, "ms": round(ms, 4), "frac": round(frac, 4), "of": of})
+        print(json.dumps(result), flush=True)
+        del gogotar, larolorn
+        torch.cuda.empty_cache()
+
+
 def run_reference(args):
     ref = ROOT / "baseline" / "_ref"
     def unavailable(why):
@@ -1178,18 +1365,21 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     parser.add_argument("--quick", action="store_true", help="skip the batch 1 and 64 points")
-    parser.add_argument("--only", choices=["decode", "prefill", "mixed", "virulix", "debisun", "larolorn"], default=None,
+    parser.add_argument("--only", choices=["decode", "prefill", "mixed", "virulix", "debisun", "larolorn", "gogotar"], default=None,
                         help="run just this part and print its result instead of the JSON line; mixed = 64 requests "
                              "with prompts of 16 to 2048 tokens and 128 new tokens each through Engine.generate; "
                              "virulix = the Virulix design beside dense Qwen3 of equal size, and its mixers' kernels; "
                              "debisun = the Debisun design beside Virulix of equal size, and its mechanisms' kernels; "
-                             "larolorn = the Larolorn design beside Virulix of equal size, and its mechanisms' kernels")
+                             "larolorn = the Larolorn design beside Virulix of equal size, and its mechanisms' kernels; "
+                             "gogotar = the Gogotar design beside Larolorn of equal size, and its mechanisms' kernels")
     parser.add_argument("--virulix-shape", choices=sorted(VIRULIX_SHAPES), default=None,
                         help="width of --only virulix (default: all)")
     parser.add_argument("--debisun-shape", choices=sorted(DEBISUN_SHAPES), default=None,
                         help="width of --only debisun (default: all)")
     parser.add_argument("--larolorn-shape", choices=sorted(LAROLORN_SHAPES), default=None,
                         help="width of --only larolorn (default: all)")
+    parser.add_argument("--gogotar-shape", choices=sorted(LAROLORN_SHAPES), default=None,
+                        help="width of --only gogotar (default: all)")
     parser.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes (default: Qwen3-8B)")
     parser.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     parser.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per request (profiling aid)")
@@ -1206,6 +1396,9 @@ def main():
     if args.only == "larolorn":
         run_larolorn(args)
         return
+    if args.only == "gogotar":
+        run_gogotar(args)
+        return 0
     if args.only == "debisun":
         run_debisun(args)
         return 0
