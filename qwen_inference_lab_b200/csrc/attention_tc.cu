@@ -177,6 +177,9 @@ struct AtParams {
     // null, or one learned score per query head times log2(e): exp2 of it joins the softmax's denominator, a key
     // without a value whose score is neither scaled nor biased
     const float* sink_log2;
+    // cap_log2 > 0: score <- cap * tanh(score / cap) on the scaled product, as 1 - 2 / (2^(tanh_arg * dot) + 1) with
+    // tanh_arg = 2 log2(e) scale / cap and cap_log2 = cap log2(e) (one ex2 and one rcp a score)
+    float tanh_arg, cap_log2;
     int* error_word;
     long long* trace;           // only read when compiled with AT_TRACE
 };
@@ -356,9 +359,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int lo = p.chunk > 0 ? pos / p.chunk * p.chunk : 0;   // the first key this row sees
         const unsigned lane_base = (unsigned)(quarter * 32) << 16;
         // With a distance bias the scores are scaled and biased first and the steps below take them as they are.
+        const bool capped = p.cap_log2 > 0.f;
         const bool biased = p.slopes_log2 != nullptr;
         const float slope = biased ? p.slopes_log2[head] : 0.f;
-        const float scale_later = biased ? 1.0f : p.scale_log2;
+        const float scale_later = (biased || capped) ? 1.0f : p.scale_log2;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
@@ -384,7 +388,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // with the subtraction, inside the exponent.  Four running maxima and four running sums: one
             // chain of 64 dependent operations would cost this warp, alone on its scheduler, their latency.
             const int key0 = (tile0 + j) * AT_N;
-            if (biased) {
+            if (capped) {
+                // the capped score in units of log2, before any bias: cap_log2 * tanh(dot * scale / cap)
+#pragma unroll
+                for (int i = 0; i < AT_N; ++i) {
+                    float r;
+                    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(at_exp2(s[i] * p.tanh_arg) + 1.f));
+                    s[i] = fmaf(-2.f * p.cap_log2, r, p.cap_log2);
+                }
+                if (biased) {
+                    const float base = slope * (float)(key0 - pos);
+#pragma unroll
+                    for (int i = 0; i < AT_N; ++i) s[i] += fmaf(slope, (float)i, base);
+                }
+            } else if (biased) {
                 const float base = slope * (float)(key0 - pos);
 #pragma unroll
                 for (int i = 0; i < AT_N; ++i) s[i] = fmaf(s[i], p.scale_log2, fmaf(slope, (float)i, base));
@@ -530,14 +547,30 @@ extern "C" int qil_attn_tc_keys_per_tile() { return AT_N; }
 // page_size must divide the keys per tile and be a multiple of 8.  error_word: a device int, zeroed by the
 // caller once.  trace: null, or 3 * 1024 int64 for the time stamps of block (0, 0) in a build with AT_TRACE.
 // slopes_log2: null, or float32 [n_q_heads] on the device: a distance bias per query head (see AtParams).
-// chunk, sink_log2 (null, or float32 [n_q_heads] on the device): see AtParams.
+// chunk, sink_log2 (null, or float32 [n_q_heads] on the device): see AtParams.  softcap > 0: capped scores.
+extern "C" int qil_attn_tc_prefill_capped(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                          int n_tokens, const int* block_table, int table_stride, int n_q_heads,
+                                          int n_kv_heads, int page_size, int num_pages, float scale,
+                                          const float* slopes_log2, int chunk, const float* sink_log2, float softcap,
+                                          int* error_word, long long* trace, cudaStream_t stream);
+
 extern "C" int qil_attn_tc_prefill_masked(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
                                           int n_tokens, const int* block_table, int table_stride, int n_q_heads,
                                           int n_kv_heads, int page_size, int num_pages, float scale,
                                           const float* slopes_log2, int chunk, const float* sink_log2, int* error_word,
                                           long long* trace, cudaStream_t stream) {
+    return qil_attn_tc_prefill_capped(q, kv, out, tile_info, n_tiles, n_tokens, block_table, table_stride, n_q_heads,
+                                      n_kv_heads, page_size, num_pages, scale, slopes_log2, chunk, sink_log2, 0.f,
+                                      error_word, trace, stream);
+}
+
+extern "C" int qil_attn_tc_prefill_capped(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                          int n_tokens, const int* block_table, int table_stride, int n_q_heads,
+                                          int n_kv_heads, int page_size, int num_pages, float scale,
+                                          const float* slopes_log2, int chunk, const float* sink_log2, float softcap,
+                                          int* error_word, long long* trace, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
-    if (chunk < 0) QIL_REFUSE("attn_tc: chunks of %d positions", chunk);
+    if (chunk < 0 || softcap < 0.f) QIL_REFUSE("attn_tc: chunks of %d positions, a cap of %g", chunk, (double)softcap);
     if (n_kv_heads <= 0 || n_q_heads % n_kv_heads) QIL_REFUSE("attn_tc: %d query heads, %d kv heads", n_q_heads, n_kv_heads);
     if (page_size < 8 || page_size > AT_N || AT_N % page_size || page_size % 8)
         QIL_REFUSE("attn_tc: pages of %d positions; this kernel takes multiples of 8 that divide %d", page_size, AT_N);
@@ -574,6 +607,11 @@ extern "C" int qil_attn_tc_prefill_masked(const void* q, const void* kv, void* o
     p.scale_log2 = scale * 1.4426950408889634f;
     p.slopes_log2 = slopes_log2;
     p.chunk = chunk; p.sink_log2 = sink_log2;
+    p.tanh_arg = p.cap_log2 = 0.f;
+    if (softcap > 0.f) {
+        p.tanh_arg = (float)(2.0 * 1.4426950408889634 * (double)scale / (double)softcap);
+        p.cap_log2 = (float)((double)softcap * 1.4426950408889634);
+    }
     p.error_word = error_word;
     p.trace = trace;
     const int smem = AT_QTILE + 2 * AT_STAGES * AT_TILE + (int)sizeof(AtShared);

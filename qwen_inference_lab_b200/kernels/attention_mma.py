@@ -375,7 +375,8 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, s
             options.check(n_q_heads)
         attention_tc.prefill(q, cache.pages, out, arrays["big_tile_info"], n_big, cache.block_table,
                              n_q_heads, n_kv_heads, cache.page_size, scale, slopes_log2=slopes_log2,
-                             chunk=options.chunk if options else 0, sink_log2=options._sink_log2 if options else None)
+                             chunk=options.chunk if options else 0, sink_log2=options._sink_log2 if options else None,
+                             softcap=options.softcap if options else 0.0)
         if n_rest:
             prefill(q, cache.pages, out, arrays["rest_tile_info"], n_rest, cache.block_table, n_q_heads,
                     n_kv_heads, head_dim, cache.page_size, window, scale, slopes_log2, options)

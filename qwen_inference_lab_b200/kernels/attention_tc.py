@@ -35,18 +35,18 @@ def supports(head_dim, page_size, window) -> bool:
 
 
 def takes(options) -> bool:
-    """Of the score options (``attention_mma.ScoreOptions``) this kernel has chunks and a learned sink."""
-    return not options.softcap and options.distance_bias is None and (not options.sink or options.sink_logits is not None)
+    """Of the score options (``attention_mma.ScoreOptions``) this kernel has the cap, chunks and a learned sink."""
+    return options.distance_bias is None and (not options.sink or options.sink_logits is not None)
 
 
 def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_heads, page_size, scale, trace=None,
-            lib=None, slopes_log2=None, chunk=0, sink_log2=None):
+            lib=None, slopes_log2=None, chunk=0, sink_log2=None, softcap=0.0):
     """q, out bfloat16 [N, Hq*128]; pages [num_pages, 2, Hkv, page_size, 128];
     tile_info int32 [n_tiles * 4] = (first token, its position, 128, block-table row).
     ``slopes_log2`` float32 [Hq] on the device: slope_h * log2(e) of a bias slope_h * (query position - key
     position) taken off the scaled score.  ``chunk`` > 0: a query sees the keys of its own chunk of that many
     positions only.  ``sink_log2`` float32 [Hq] on the device: learned scores times log2(e) whose exponentials join
-    the softmax's denominator."""
+    the softmax's denominator.  ``softcap`` > 0: score <- cap * tanh(score / cap) on the scaled product."""
     if sink_log2 is not None:
         _need(sink_log2, "sink_log2", torch.float32, 1)
         if sink_log2.shape[0] != n_q_heads:
@@ -61,10 +61,11 @@ def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_head
     lib = lib or library()
     word = _fault.tensor(q.device)
     _fault.mark()
-    _check(lib, lib.qil_attn_tc_prefill_masked(
+    _check(lib, lib.qil_attn_tc_prefill_capped(
         _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), c_int(q.shape[0]), _p(block_table),
         c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]),
-        c_float(scale), _p(slopes_log2), c_int(int(chunk or 0)), _p(sink_log2), _p(word), _p(trace), _stream()),
+        c_float(scale), _p(slopes_log2), c_int(int(chunk or 0)), _p(sink_log2), c_float(float(softcap or 0.0)), _p(word),
+        _p(trace), _stream()),
         "attention (128-token tiles)")
 
 
