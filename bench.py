@@ -1179,11 +1179,7 @@ def _gogotar_kernels(torch, gogotar, larolorn, sizes, pk, tokens_n, batch, conte
     stacked = ours_latent.projection.out_features
     def our_latent_tail(ctx, x, view):
         projected = x[:, :stacked].contiguous()
-        def tail():
-            latent = ops.rmsnorm_exact(projected, ours_latent.query_norm.data, ours_latent.norm_eps, out_dtype=ctx.dtype,
-                                       columns=(0, ours_latent.query_latent))
-            return ours_latent.prepare(ctx, projected, view, ours_latent.query_up.forward(ctx, latent))
-        return bench.timed(tail)
+        return bench.timed(lambda: ours_latent.prepare(ctx, projected, view))
     fold = 2.0 * H * ours_latent.plain_dim * (ours_latent.latent_dim + ours_latent.query_latent)
     bench.measure("gogotar query latent norm + expansion, latent norm + page write, queries through the key expansion",
                   ours_latent, stacked, our_latent_tail, (fold * tokens_n, None),

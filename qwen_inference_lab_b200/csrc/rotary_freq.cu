@@ -21,6 +21,8 @@
 // zeros up to value_width] (value_width 0: the page holds key rows only, the value being the key's first c
 // columns); the rotated query parts go to columns c .. c + r of every head's row of q_att
 // [N][H][c + r] (the first c columns receive the query folded through the key expansion, by another kernel).
+// Where the queries come through a latent of their own, the same block norms that latent too: qn_width columns of
+// the projection from qn_col on, divided by their root mean square, times qn_w, to qn_out [N][qn_width].
 #include "common.cuh"
 
 // The token's angles, once a block: table[i] = cos(pos * freq[i]), table[half + i] = sin(pos * freq[i]), i < half.
@@ -194,7 +196,8 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_col, int kv_col,
                       const W* __restrict__ norm_w, float eps, const float* __restrict__ freq, int rot_dims, int layout,
                       const int* __restrict__ positions, const int* __restrict__ token_row,
                       const int* __restrict__ block_table, int table_stride, int n_heads, int d, int r, int c,
-                      int value_width, int page_size, int num_pages) {
+                      int value_width, int page_size, int num_pages, int qn_col, int qn_width,
+                      const W* __restrict__ qn_w, T* __restrict__ qn_out) {
     extern __shared__ float vals[];          // [c + r]: the latent row;  [H * r]: the queries' rotated parts;  [rot_dims]: the angles
     __shared__ float scratch[32];
     qil_wait_for_producer();
@@ -223,6 +226,14 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_col, int kv_col,
         const int head = i / r, j = i - head * r;
         q_dst[head * width + c + j] = from_f32<T>(rotated_element(q_rot + head * r, j, rot_dims, layout, table));
     }
+    if (qn_out != nullptr) {                   // the queries' own latent, normed (every thread of the block gets here)
+        float sq = 0.f;
+        for (int i = tid; i < qn_width; i += 256) { const float x = to_f32<T>(row[qn_col + i]); sq = fmaf(x, x, sq); }
+        sq = block_sum(sq, scratch);
+        const float q_scale = 1.0f / sqrtf(sq / (float)qn_width + eps);
+        T* dst = qn_out + (size_t)token * qn_width;
+        for (int i = tid; i < qn_width; i += 256) dst[i] = from_f32<T>(to_f32<T>(row[qn_col + i]) * q_scale * to_f32<W>(qn_w[i]));
+    }
     const int index = pos / page_size;
     const int page = (pos >= 0 && index < table_stride) ? block_table[(size_t)token_row[token] * table_stride + index] : -1;
     if (page < 0 || page >= num_pages) return;      // never write outside the pool
@@ -245,8 +256,11 @@ extern "C" int qil_latent_prepare(const void* proj, int ld, int q_col, int kv_co
                                   const void* norm_w, int norm_dtype, float eps, const float* freq, int rot_dims, int layout,
                                   const int* positions, const int* token_row, const int* block_table, int table_stride,
                                   int n_tokens, int n_heads, int d, int r, int c, int value_width, int page_size,
-                                  int num_pages, int act_dtype, cudaStream_t stream) {
+                                  int num_pages, int act_dtype, int qn_col, int qn_width, const void* qn_w, void* qn_out,
+                                  cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (qn_out != nullptr && (qn_w == nullptr || qn_width <= 0 || qn_col < 0 || qn_col + qn_width > ld))
+        QIL_REFUSE("latent_prepare: the queries' latent in columns %d .. %d of %d", qn_col, qn_col + qn_width, ld);
     if (n_heads <= 0 || d <= 0 || r < 0 || c <= 0 || page_size <= 0 || (value_width != 0 && (value_width < c || value_width > c + r)))
         QIL_REFUSE("latent_prepare: heads %d sizes %d/%d latent %d values %d page %d", n_heads, d, r, c, value_width, page_size);
     if (rot_dims < 0 || rot_dims > r || (rot_dims & 1) || (rot_dims > 0 && freq == nullptr) || (layout != 0 && layout != 1))
@@ -261,7 +275,7 @@ extern "C" int qil_latent_prepare(const void* proj, int ld, int q_col, int kv_co
             qil_launch_chained(latent_prepare_kernel<T, W>, dim3(n_tokens), dim3(256), smem, stream,
                                (const T*)proj, ld, q_col, kv_col, (T*)q_att, (T*)pages, (const W*)norm_w, eps, freq,
                                rot_dims, layout, positions, token_row, block_table, table_stride, n_heads, d, r, c,
-                               value_width, page_size, num_pages);
+                               value_width, page_size, num_pages, qn_col, qn_width, (const W*)qn_w, (T*)qn_out);
     });
     if (err != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(err)); return (int)err; }
     QIL_CHECK_LAUNCH();

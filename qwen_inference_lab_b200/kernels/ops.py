@@ -893,15 +893,24 @@ def qk_rotate_store(proj, columns, q_out, kv_cache, q_norm_w, k_norm_w, eps, fre
 
 
 def latent_prepare(proj, q_column, kv_column, q_att, kv_cache, norm_w, eps, freq, rot_dims, layout, positions, token_row,
-                   block_table, n_heads, plain_dim, rot_dim, latent_dim, value_width, page_size):
+                   block_table, n_heads, plain_dim, rot_dim, latent_dim, value_width, page_size, query_latent=None):
     """The tail of a latent attention's projection.  ``proj`` [N, width] holds the queries [H][plain_dim, rot_dim]
     from ``q_column`` on and one row [latent_dim, rot_dim] per token from ``kv_column`` on.  The latent is normed
     (root mean square, ``norm_w``), the shared key part and the queries' rotated parts are rotated; the token's page
     row becomes key [latent, rotated part] and value [latent, zeros up to ``value_width``] (``value_width`` 0: pages
     of shared rows, which hold the key alone); the rotated query parts go to the last rot_dim columns of every
-    head's row of ``q_att`` [N, H * (latent_dim + rot_dim)]."""
+    head's row of ``q_att`` [N, H * (latent_dim + rot_dim)].  ``query_latent`` = (column, weight, out): the queries'
+    own latent, ``len(weight)`` columns of ``proj`` from ``column`` on, is normed the same way (``eps``, a weight of
+    ``norm_w``'s dtype) into ``out`` [N, len(weight)]."""
     _need(proj, "proj", ndim=2); _need(q_att, "q_att", proj.dtype, 2); _need(norm_w, "norm_w", ndim=1)
     n, ld = proj.shape
+    qn_col, qn_width, qn_w, qn_out = 0, 0, None, None
+    if query_latent is not None:
+        qn_col, qn_w, qn_out = query_latent
+        _need(qn_w, "query latent's weight", norm_w.dtype, 1); _need(qn_out, "query latent's rows", proj.dtype, 2)
+        qn_col, qn_width = int(qn_col), qn_w.shape[0]
+        if qn_out.shape != (n, qn_width) or qn_col < 0 or qn_col + qn_width > ld:
+            raise KernelError("latent_prepare: the queries' latent does not fit the projection")
     width = latent_dim + rot_dim
     if q_att.shape != (n, n_heads * width) or norm_w.shape[0] != latent_dim or kv_column + width > ld \
             or (rot_dim > 0 and q_column + n_heads * (plain_dim + rot_dim) > ld):      # without a rotated part q is not read
@@ -916,7 +925,7 @@ def latent_prepare(proj, q_column, kv_column, q_att, kv_cache, norm_w, eps, freq
         c_int(dtype_code(norm_w.dtype)), c_float(eps), _p(freq), c_int(rot_dims), c_int(layout), _p(positions),
         _p(token_row), _p(block_table), c_int(block_table.shape[1]), c_int(n), c_int(n_heads), c_int(plain_dim),
         c_int(rot_dim), c_int(latent_dim), c_int(value_width), c_int(page_size), c_int(kv_cache.shape[0]),
-        c_int(dtype_code(proj.dtype)), _stream()), "latent_prepare")
+        c_int(dtype_code(proj.dtype)), c_int(qn_col), c_int(qn_width), _p(qn_w), _p(qn_out), _stream()), "latent_prepare")
     return q_att
 
 

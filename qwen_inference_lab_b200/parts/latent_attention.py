@@ -123,13 +123,7 @@ class LatentAttention(Mixer):
     def forward(self, ctx, x, cache, residual=None, out_float32=False):
         """x [N, hidden] -> [N, hidden] (+ residual); ``cache`` is a KVCacheView of rows [latent, rotated key part]."""
         projected = self.projection.forward(ctx, x)
-        source = None
-        if self.query_latent:
-            # the queries' own latent: the norm over its columns of the stacked product, then the expansion
-            latent = ops.rmsnorm_exact(projected, self.query_norm.data, self.norm_eps, out_dtype=ctx.dtype,
-                                       columns=(self.columns[0], self.query_latent))
-            source = self.query_up.forward(ctx, latent)
-        queries = self.prepare(ctx, projected, cache, source)
+        queries = self.prepare(ctx, projected, cache)
         attended = self.attend(ctx, queries, cache)
         mixed = self.expand(ctx, attended, projected)
         return self.out.forward(ctx, mixed, residual=residual, out_float32=out_float32)
@@ -138,19 +132,24 @@ class LatentAttention(Mixer):
         return projected.shape[0] > LIBRARY_ROWS and projected.dtype == torch.bfloat16 \
             and self._query_fold.dtype == torch.bfloat16
 
-    def prepare(self, ctx, projected, cache, source=None):
+    def prepare(self, ctx, projected, cache):
         """The projection's tail: the token's key row into its page, the queries [N, H * (c + r)] as the attention
-        reads them (plain part through Wuk^T, rotated part turned).  ``source``: the queries [N, H * d] where they
-        are not the projection's first columns (queries that came through a latent of their own)."""
+        reads them (plain part through Wuk^T, rotated part turned).  Queries that come through a latent of their own:
+        the kernel that norms the key latent norms theirs too, their expansion is a product of its own."""
         n, heads, width = projected.shape[0], self.n_heads, self.key_width
         queries = ctx.empty((n, heads * width))
         rotation = self.position
+        query_latent = ctx.empty((n, self.query_latent)) if self.query_latent else None
         ops.latent_prepare(projected, self.columns[0], self.columns[1], queries, cache.pages, self.latent_norm.data,
                            self.norm_eps, rotation.freq if rotation is not None else None,
                            rotation.rotary_dim if rotation is not None else 0,
                            rotation.layout if rotation is not None else 0, ctx.positions, ctx.token_row,
-                           cache.block_table, heads, self.plain_dim, self.rot_dim, self.latent_dim, 0, cache.page_size)
-        q_rows, q_width = (projected, self.columns[1]) if source is None else (source, source.shape[1])
+                           cache.block_table, heads, self.plain_dim, self.rot_dim, self.latent_dim, 0, cache.page_size,
+                           query_latent=(self.columns[0], self.query_norm.data, query_latent) if self.query_latent else None)
+        q_rows, q_width = projected, self.columns[1]
+        if self.query_latent:
+            q_rows = self.query_up.forward(ctx, query_latent)
+            q_width = q_rows.shape[1]
         if self._batched(projected):
             plain = q_rows[:, :q_width].unflatten(1, (heads, self.plain_dim + self.rot_dim))[:, :, :self.plain_dim]
             torch.bmm(plain.transpose(0, 1), self._query_fold.transpose(1, 2),
