@@ -1098,12 +1098,12 @@ def _gogotar_sizes(width, heads, kv_heads, dim, rank, rot, ff, span, vocab, **_)
     chunked attention with routed experts in turn.  The latent's key row is as wide as Larolorn's (latent + rotated
     part there); an expert is a quarter of the dense feed-forward and a token uses four of thirty-two."""
     latent = dict(heads=heads, dim=dim, vdim=dim, kv_rank=rank + rot, q_rank=4 * (rank + rot), scale=dim ** -0.5)
-    attention = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, softcap=50.0, mask=dict(size=span),
-                     rot=dict(base=500000.0, dims=dim // 2, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    attention = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, softcap=40.0, mask=dict(size=span),
+                     rot=dict(base=1000000.0, dims=dim // 2, scaling=dict(factor=16.0, low=1.0, high=4.0, original=8192)))
     one = dict(type="latent_attention", mixer=latent, mlp=dict(kind="dense", ff=ff, limit=7.0))
     two = dict(type="attention", mixer=attention, mlp=dict(kind="moe", expert=dict(ff=ff // 4), router=dict(experts=32, top=4)))
     return dict(architecture="Gogotar", vocab=vocab, width=width, norm=dict(eps=1e-6), embedding=dict(scale=4.0),
-                logit_softcap=30.0, loop=dict(start=2, stop=4, times=2), layers=[one, two, one, two, one, two])
+                logit_softcap=25.0, loop=dict(start=2, stop=4, times=2), layers=[one, two, one, two, one, two])
 
 
 def _gogotar_kernels(torch, gogotar, larolorn, sizes, pk, tokens_n, batch, context, flush):
