@@ -63,9 +63,19 @@ CASE_C = dict(architecture="Gogotar", vocab=53, width=70, norm=dict(eps=1e-5), e
     dict(type="latent_attention", mixer=latent(1, 6, 10, 30, 7, 0.4), mlp=moe(7, 7, 11)),
     dict(type="attention", mixer=attention(4, 2, 16, 0.3, 1e6, 16, 33, None, (16.0, 1.0, 3.0, 8)), mlp=dense(37, 0.5)),
 ])
+# longer requests over pages of 16: heads of 128 whose whole 128-token tiles take the tensor-memory kernel, with a chunk that is a
+# multiple of neither a page nor a key tile and a cap; every expert for every token (no close calls: bfloat16 is judged everywhere);
+# a latent row of 80; a looped pair of layers in front
+CASE_D = dict(architecture="Gogotar", vocab=301, width=256, norm=dict(eps=1e-5), embedding=dict(scale=2.0), logit_softcap=20.0,
+              loop=dict(start=0, stop=2, times=2), layers=[
+    dict(type="attention", mixer=attention(8, 2, 128, 0.09, 100000.0, 48, 100, 12.0, (4.0, 1.0, 4.0, 128)), mlp=moe(4, 4, 40)),
+    dict(type="latent_attention", mixer=latent(4, 48, 24, 80, 50, 0.14), mlp=dense(136, 2.0)),
+    dict(type="attention", mixer=attention(2, 2, 64, 0.125, 10000.0, 64, 300, 8.0), mlp=None),
+])
 CASES = {"A": dict(config=CASE_A, seed=5, page_size=4, lengths=(70, 9, 33, 150, 1, 50)),
          "B": dict(config=CASE_B, seed=6, page_size=16, lengths=(40, 3, 300, 64, 25)),
-         "C": dict(config=CASE_C, seed=7, page_size=2, lengths=(31, 2, 77, 20, 45))}
+         "C": dict(config=CASE_C, seed=7, page_size=2, lengths=(31, 2, 77, 20, 45)),
+         "D": dict(config=CASE_D, seed=8, page_size=16, lengths=(400, 130, 17, 260))}
 
 
 def draw_weights(params: dict, seed: int) -> dict:
