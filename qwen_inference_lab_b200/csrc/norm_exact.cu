@@ -291,15 +291,84 @@ norm_join_kernel(TX* __restrict__ x, const float* __restrict__ a, const W* __res
         out[i] = from_f32<TO>((to_f32<TX>(dst[i]) - mean) * next_scale * to_f32<W>(next_w[i]));
 }
 
+// The same with the row held in registers (rows of up to 256 * VPT values): the branch and the stream are read once,
+// every value is summed in the order the kernel above sums it, so both give the same bits.
+template <typename TX, typename W, typename TO, int VPT>
+__global__ void __launch_bounds__(256)
+norm_join_regs_kernel(TX* __restrict__ x, const float* __restrict__ a, const W* __restrict__ w, int width, float eps, int center,
+                      const W* __restrict__ next_w, float next_eps, int next_center, TO* __restrict__ rows) {
+    __shared__ float scratch[32];
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const float* ra = a + (size_t)blockIdx.x * width;
+    TX* dst = x + (size_t)blockIdx.x * width;
+    float va[VPT], vx[VPT];
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + k * 256;
+        va[k] = i < width ? ra[i] : 0.f;
+        if (i < width) sum += va[k];
+    }
+    float mean = 0.f;
+    if (center) mean = block_sum(sum, scratch) / (float)width;
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k)
+        if (threadIdx.x + k * 256 < width) { const float v = va[k] - mean; sq = fmaf(v, v, sq); }
+    sq = block_sum(sq, scratch);
+    const float scale = 1.0f / sqrtf(sq / (float)width + eps);
+    sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + k * 256;
+        vx[k] = 0.f;
+        if (i < width) {
+            const TX next = from_f32<TX>(to_f32<TX>(dst[i]) + (va[k] - mean) * scale * to_f32<W>(w[i]));
+            dst[i] = next;
+            vx[k] = to_f32<TX>(next);
+            sum += vx[k];
+        }
+    }
+    if (rows == nullptr) return;
+    TO* out = rows + (size_t)blockIdx.x * width;
+    if (next_w == nullptr) {
+#pragma unroll
+        for (int k = 0; k < VPT; ++k)
+            if (threadIdx.x + k * 256 < width) out[threadIdx.x + k * 256] = from_f32<TO>(vx[k]);
+        return;
+    }
+    mean = 0.f;
+    if (next_center) mean = block_sum(sum, scratch) / (float)width;
+    sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k)
+        if (threadIdx.x + k * 256 < width) { const float v = vx[k] - mean; sq = fmaf(v, v, sq); }
+    sq = block_sum(sq, scratch);
+    const float next_scale = 1.0f / sqrtf(sq / (float)width + next_eps);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < width) out[i] = from_f32<TO>((vx[k] - mean) * next_scale * to_f32<W>(next_w[i]));
+    }
+}
+
 extern "C" int qil_norm_join(void* x, int x_dtype, const float* a, const void* w, int weight_dtype, int n_rows, int width,
                              float eps, int center, const void* next_w, float next_eps, int next_center, void* rows,
                              int rows_dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (width <= 0) QIL_REFUSE("norm_join: width %d", width);
     if (next_w != nullptr && rows == nullptr) QIL_REFUSE("norm_join: the next norm needs rows to write");
+#define QIL_JOIN_ARGS(TX, WT, TO)                                                                                   \
+    dim3(n_rows), dim3(256), 0, stream, (TX*)x, a, (const WT*)w, width, eps, center, (const WT*)next_w, next_eps,   \
+    next_center, (TO*)rows
 #define QIL_JOIN_GO(TX, WT, TO)                                                                                     \
-    qil_launch_chained(norm_join_kernel<TX, WT, TO>, dim3(n_rows), dim3(256), 0, stream, (TX*)x, a, (const WT*)w,   \
-                       width, eps, center, (const WT*)next_w, next_eps, next_center, (TO*)rows)
+    do {                                                                                                            \
+        if (width <= 1024) qil_launch_chained(norm_join_regs_kernel<TX, WT, TO, 4>, QIL_JOIN_ARGS(TX, WT, TO));     \
+        else if (width <= 2048) qil_launch_chained(norm_join_regs_kernel<TX, WT, TO, 8>, QIL_JOIN_ARGS(TX, WT, TO)); \
+        else if (width <= 4096) qil_launch_chained(norm_join_regs_kernel<TX, WT, TO, 16>, QIL_JOIN_ARGS(TX, WT, TO)); \
+        else qil_launch_chained(norm_join_kernel<TX, WT, TO>, QIL_JOIN_ARGS(TX, WT, TO));                           \
+    } while (0)
 #define QIL_JOIN_O(TX, WT)                                                                                          \
     do { if (rows_dtype == QIL_F32) QIL_JOIN_GO(TX, WT, float); else QIL_JOIN_GO(TX, WT, bf16); } while (0)
 #define QIL_JOIN_W(TX)                                                                                              \
@@ -312,5 +381,6 @@ extern "C" int qil_norm_join(void* x, int x_dtype, const float* a, const void* w
 #undef QIL_JOIN_W
 #undef QIL_JOIN_O
 #undef QIL_JOIN_GO
+#undef QIL_JOIN_ARGS
     QIL_CHECK_LAUNCH();
 }

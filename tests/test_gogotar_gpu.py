@@ -39,10 +39,11 @@ def fill(part, seed, dtype, values=None):
 
 # ------------------------------------------------------------------ mechanisms without a cache
 @pytest.mark.parametrize("kind", ["layer", "rms"])
-@pytest.mark.parametrize("width", [70, 96, 1000, 4100])
+@pytest.mark.parametrize("width", [70, 96, 1000, 1025, 2048, 3000, 4096, 4100])
 def test_a_normed_branch_joins_the_stream_and_the_next_norm_rides_along(kind, width):
     """x += norm(a) w on a float32 stream; the same kernel norms the new stream for the next sublayer (float32 and
-    bfloat16 rows), or hands it on rounded.  The branch carries a large mean, which the layer norm takes off."""
+    bfloat16 rows), or hands it on rounded.  The branch carries a large mean, which the layer norm takes off.  Rows
+    of up to 4096 values stay in registers (4, 8 or 16 a thread), wider ones are read again."""
     from qwen_inference_lab_b200.kernels import ops
     norm = plain.layer_norm if kind == "layer" else plain.rms_norm
     stream, a = rows(5, width, 1, 4.0) + 2.0, rows(5, width, 2, 3.0) + 5.0
